@@ -1,0 +1,202 @@
+/*
+ * mugen_mla.h — C ABI of the B200 (sm_100a) implementation of Mugen's MLA absorbed-attention
+ * decode path over its compressed latent KV cache.
+ *
+ * This is the drop-in boundary.  The reference has no FFI layer for this path: it is private
+ * C++ inside mugen::TransformerModel::Impl.  Each entry point below therefore cites the piece
+ * of reference code whose job it takes over (paths relative to the reference tree).  Plain
+ * pointers and sizes only; a CUDA stream travels as void* (cudaStream_t).  All functions
+ * return MLA_OK (0) or an error code; mla_last_error() gives the text.  There is no CPU
+ * fallback: without a CUDA device mla_create fails.
+ *
+ * Element types: the latent cache, q, kv_a and the output use one storage type per context,
+ * IEEE half (the reference's mugen::f16, include/mugen/core/types.h:10) or bfloat16.
+ *
+ * Latent cache row (src/core/model/transformer.cpp:3396-3400): 576 values per token per layer
+ * = c_kv[512] (RMS-normalised) followed by k_rope[64] (RoPE applied).  Rows live in fixed
+ * pages of 64 tokens; a page id names the same slot range in every layer.
+ *
+ * Threading: one host thread per context; calls are stream-ordered and asynchronous.
+ */
+#ifndef MUGEN_MLA_H
+#define MUGEN_MLA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mla_ctx mla_ctx;
+
+enum {
+    MLA_OK = 0,
+    MLA_ERR_INVALID = 1,      /* bad argument */
+    MLA_ERR_CUDA = 2,         /* a CUDA runtime/driver call failed */
+    MLA_ERR_NO_PAGES = 3,     /* page pool exhausted */
+    MLA_ERR_CAPACITY = 4,     /* position beyond max_seq_len, or too many rows/sequences */
+    MLA_ERR_STATE = 5,        /* call out of order (e.g. decode without step_begin) */
+    MLA_ERR_DEVICE = 6,       /* a kernel reported a fault through the status word */
+    MLA_ERR_UNSUPPORTED = 7   /* shape or type this build does not handle */
+};
+
+enum { MLA_DTYPE_F16 = 0, MLA_DTYPE_BF16 = 1 };
+
+/* Weight encodings accepted by mla_set_layer_weights: GGML type ids as the reference's
+ * dequant_weight_row understands them (src/core/model/transformer.cpp:2489-2534,
+ * src/model/ggml_types.h:12-40), plus BF16. */
+enum { MLA_W_F16 = 1, MLA_W_Q4_0 = 2, MLA_W_Q8_0 = 8, MLA_W_BF16 = 30 };
+
+enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2 };
+
+/* Shape contract: the MLA fields of mugen::ModelConfig (src/core/model/transformer.h:65-79)
+ * plus the paged-pool geometry the reference lacks (it keeps one contiguous
+ * [max_seq_len][576] buffer per layer, transformer.cpp:3396-3407). */
+typedef struct mla_config {
+    uint32_t n_layers;
+    uint32_t n_heads;
+    uint32_t kv_lora_rank;        /* must be 512 */
+    uint32_t qk_nope_head_dim;    /* must be 128 */
+    uint32_t qk_rope_head_dim;    /* must be 64  */
+    uint32_t v_head_dim;          /* must be 128 */
+    float    rope_theta;
+    float    rms_norm_eps;
+    float    rope_scaling_factor; /* YaRN factor; <= 1 means plain RoPE */
+    uint32_t rope_original_ctx;
+    uint32_t max_seq_len;         /* per-sequence capacity in tokens */
+    uint32_t page_tokens;         /* must be 64 */
+    uint32_t n_pages;             /* pages in the pool (each page spans all layers) */
+    uint32_t max_seqs;            /* live sequences */
+    uint32_t max_rows;            /* query rows (new tokens) per step; 0 -> max_seqs */
+    uint32_t dtype;               /* MLA_DTYPE_* */
+    int32_t  device;              /* CUDA device ordinal */
+    uint32_t kernel;              /* MLA_KERNEL_* */
+    uint32_t max_position;        /* highest global position + 1 (rotary table rows);
+                                     0 -> max_seq_len.  Larger than max_seq_len only for
+                                     KV-range shards, whose rows start at a base position */
+} mla_config;
+
+/* ---- lifetime ------------------------------------------------------------------------- */
+
+/* Replaces model-init steps: KVCache::create (src/core/memory/kv_cache.cpp:146-159; same
+ * validation messages), the per-layer latent buffer allocation (transformer.cpp:3396-3407)
+ * and the score scratch (transformer.cpp:3411-3412). */
+int mla_create(const mla_config* cfg, mla_ctx** out);
+void mla_destroy(mla_ctx* ctx);
+/* Text of the last error on this context (or of the last failed mla_create when ctx is NULL). */
+const char* mla_last_error(const mla_ctx* ctx);
+/* Reads and clears the device status word that kernels set instead of trapping
+ * (0 = clean).  Synchronises the given stream. */
+int mla_status(mla_ctx* ctx, void* stream, uint32_t* device_status);
+
+/* Registers W_UK and W_UV, each (n_heads*128) x 512 row-major in `w_type`, and the c_kv
+ * RMSNorm weight [512] in the context dtype, all HOST pointers.  Replaces the k_b / v_b /
+ * kv_a_norm loading and split (transformer.cpp:3148-3221) and the per-call
+ * dequant_weight_row (:2489-2534): quantised rows are decoded once, here. Unknown types are
+ * rejected (the reference zero-fills them with a warning, :2529-2533). */
+int mla_set_layer_weights(mla_ctx* ctx, uint32_t layer, const void* w_uk, const void* w_uv,
+                          uint32_t w_type, const void* kv_norm);
+
+/* ---- sequences: the KVCache bookkeeping contract ---------------------------------------- */
+/* The reference cache holds ONE implicit sequence and, for MLA, is only a length counter
+ * (kv_cache.h:20-47; kv_cache.cpp:281-285, 313-321, 343-357).  Here every call names a
+ * sequence. */
+int mla_seq_create(mla_ctx* ctx, uint32_t* seq_id);
+int mla_seq_free(mla_ctx* ctx, uint32_t seq_id);
+/* KVCache::seq_len (kv_cache.cpp:281-285). */
+int mla_seq_len(const mla_ctx* ctx, uint32_t seq_id, uint32_t* len);
+/* KVCache::advance_seq_len (kv_cache.cpp:355-357); rows must have been appended. */
+int mla_advance(mla_ctx* ctx, uint32_t seq_id, uint32_t n);
+/* KVCache::truncate (kv_cache.cpp:313-321): frees whole pages past new_len, keeps stale rows
+ * inside the last page.  Unlike the reference it never grows: new_len > seq_len is an error. */
+int mla_truncate(mla_ctx* ctx, uint32_t seq_id, uint32_t new_len);
+/* KVCache::clear (kv_cache.cpp:343-353): returns every page of the sequence. */
+int mla_clear(mla_ctx* ctx, uint32_t seq_id);
+/* Global position of the sequence's local row 0 (default 0).  A KV-range shard of a long
+ * sequence stores rows [base, base+n) locally; RoPE still uses the global position. */
+int mla_seq_set_base(mla_ctx* ctx, uint32_t seq_id, uint32_t base_pos);
+/* Number of free pages in the pool. */
+int mla_free_pages(const mla_ctx* ctx, uint32_t* n);
+/* Test/bench aid: permute the free list with a seeded shuffle so block tables come out as a
+ * random permutation of physical pages. */
+int mla_shuffle_free_pages(mla_ctx* ctx, uint64_t seed);
+/* Copies the block table (physical page ids) of a sequence to `pages` (capacity `cap`). */
+int mla_seq_pages(const mla_ctx* ctx, uint32_t seq_id, uint32_t* pages, uint32_t cap,
+                  uint32_t* n_pages);
+
+/* ---- explicit-position calls: the reference's own call shapes, batched ------------------- */
+
+/* Steps G+H of the decode driver (transformer.cpp:3930-3987; batched twin :1263-1323):
+ * RMSNorm(c_kv)*w, YaRN/NeoX RoPE(k_rope, positions[r]) and the scatter of row r to
+ * (seq_ids[r], positions[r]) of `layer`.  kv_a: DEVICE [n][576].  seq_ids/positions: HOST.
+ * Bit-exact with the reference arithmetic.  Allocates pages on demand; does not move seq_len. */
+int mla_append_rows(mla_ctx* ctx, uint32_t layer, uint32_t n, const uint32_t* seq_ids,
+                    const uint32_t* positions, const void* kv_a, void* stream);
+
+/* cpu_mla_attention (transformer.cpp:2539-2623) for n query rows at once: row r attends rows
+ * [0, attend_lens[r]) of sequence seq_ids[r].  q: DEVICE [n][n_heads][192] (post-RoPE, nope
+ * first), out: DEVICE [n][n_heads][128].  seq_ids/attend_lens: HOST. */
+int mla_attend_rows(mla_ctx* ctx, uint32_t layer, uint32_t n, const uint32_t* seq_ids,
+                    const uint32_t* attend_lens, const void* q, void* out, void* stream);
+
+/* ---- decode-step scheduler ------------------------------------------------------------- */
+/* One step = for every listed sequence, n_new[i] new tokens (NULL = 1 each: plain decode;
+ * >1: a prefill chunk, causal; 0: the sequence takes no token here but still answers the step's
+ * query with one row attending its seq_len rows — a KV-range shard that does not own the tail;
+ * its kv_a row is ignored) at positions seq_len .. seq_len+n_new-1.  step_begin reserves
+ * pages, balances the KV ranges over the SMs and uploads the step's metadata once; the
+ * per-layer calls then take only data pointers.  Ordering contract of the reference driver
+ * (transformer.cpp:3702, 3980-3996, 4401-4403): per layer append THEN attend over
+ * seq_len + (row's offset) + 1 rows; counters advance once, after all layers (step_end). */
+int mla_step_begin(mla_ctx* ctx, uint32_t n_seq, const uint32_t* seq_ids, const uint32_t* n_new,
+                   void* stream);
+/* kv_a: DEVICE [rows][576], rows ordered by sequence then position. */
+int mla_step_append(mla_ctx* ctx, uint32_t layer, const void* kv_a, void* stream);
+/* q: DEVICE [rows][n_heads][192]; out: DEVICE [rows][n_heads][128]. */
+int mla_step_attend(mla_ctx* ctx, uint32_t layer, const void* q, void* out, void* stream);
+/* Same two calls with HOST buffers: copies kv_a and q in, runs append + attend, copies out
+ * back, all on `stream` (pinned staging inside the context). */
+int mla_step_layer_host(mla_ctx* ctx, uint32_t layer, const void* kv_a_host, const void* q_host,
+                        void* out_host, void* stream);
+int mla_step_end(mla_ctx* ctx);
+/* Rows in the current step and the number of KV segments they were split into. */
+int mla_step_info(const mla_ctx* ctx, uint32_t* rows, uint32_t* segments);
+
+/* ---- KV-range sharding of one long sequence ----------------------------------------------- */
+/* Per-head partial softmax state of this shard for every row of the current step:
+ * partial DEVICE float [rows][n_heads][514] = (m, l, acc[512]) with m the running maximum of
+ * score*log2(e)/sqrt(192), l = sum 2^(s-m), acc = sum 2^(s-m) * c_kv.  A shard with no rows
+ * to attend emits (-inf, 0, 0). */
+int mla_step_attend_partial(mla_ctx* ctx, uint32_t layer, const void* q, float* partial,
+                            void* stream);
+/* Log-sum-exp merge of n_parts such partials (DEVICE float [n_parts][rows][n_heads][514],
+ * e.g. the result of an all-gather) followed by the W_UV projection
+ * (transformer.cpp:2610-2620).  out: DEVICE [rows][n_heads][128]. */
+int mla_merge_partials(mla_ctx* ctx, uint32_t layer, uint32_t n_parts, uint32_t rows,
+                       const float* partials, void* out, void* stream);
+
+/* ---- introspection used by benchmarks --------------------------------------------------- */
+/* Kernel launches issued by this context since creation. */
+int mla_launch_count(const mla_ctx* ctx, uint64_t* n);
+/* Device timing of the split-KV attention kernel alone: while enabled, every launch of that
+ * kernel is bracketed by CUDA events on the launching stream (up to 8192 launches are kept).
+ * mla_profile_read synchronises those events and returns launches and their summed duration,
+ * then clears the record. */
+int mla_profile_enable(mla_ctx* ctx, int on);
+int mla_profile_read(mla_ctx* ctx, uint32_t* launches, float* total_ms);
+/* Name of the attention kernel family in use ("mma" or "tcgen05"). */
+const char* mla_kernel_name(const mla_ctx* ctx);
+/* Reads `n` latent rows [row_begin, row_begin+n) of (layer, seq) back to HOST memory. */
+int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
+                  void* host_out, void* stream);
+/* Writes `n` ready-made latent rows (already normalised / rotated) from DEVICE memory into
+ * (layer, seq) starting at row_begin, allocating pages: bulk cache fill for benchmarks and
+ * for restoring a saved cache. */
+int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
+                   const void* dev_rows, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUGEN_MLA_H */

@@ -1,0 +1,806 @@
+// C ABI of the B200 MLA decode path (see include/mugen_mla.h): context, paged latent cache,
+// per-step scheduling metadata, kernel dispatch.  Host logic only; kernels live beside it.
+#include "../../include/mugen_mla.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../host/page_table.hpp"
+#include "../host/rope_table.hpp"
+#include "mla_launch.h"
+
+using mugen::mla::PageTable;
+using mugen::mla::Segment;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+constexpr int kMetaRing = 4;
+
+struct LayerW {
+    void* w_uk = nullptr;
+    void* w_uv = nullptr;
+    void* norm = nullptr;
+    bool set = false;
+};
+
+struct MetaBuf {
+    void* host = nullptr;       // pinned
+    cudaEvent_t done = nullptr;
+    bool in_flight = false;
+};
+
+}  // namespace
+
+struct mla_ctx {
+    mla_config cfg{};
+    int sm_count = 0;
+    uint32_t kernel = MLA_KERNEL_MMA;
+    std::unique_ptr<PageTable> pt;
+    std::string err;
+    uint64_t launches = 0;
+
+    char* pool = nullptr;           // [layers][n_pages*64][576] elements
+    uint64_t pool_slots = 0;        // token slots per layer
+    std::vector<LayerW> layers;
+    float* cos_sin = nullptr;       // device [max positions][64]
+    uint32_t cs_rows = 0;           // positions filled so far
+    uint32_t cs_cap = 0;
+
+    void* q_abs = nullptr;          // [max_rows][H][576]
+    float* recs = nullptr;          // [max_segs][H][514]
+    uint32_t max_segs = 0;
+    uint32_t workers = 1;
+    uint32_t* status_dev = nullptr;
+    void* tmap_dev = nullptr;       // CUtensorMap (128 B) for the tcgen05 path
+
+    // metadata upload ring
+    MetaBuf ring[kMetaRing];
+    int ring_next = 0;
+    size_t meta_cap = 0;
+    char* meta_dev = nullptr;
+    mla::StepMeta meta{};
+
+    // step state
+    bool in_step = false;
+    std::vector<uint32_t> step_seqs, step_nnew;
+
+    // optional per-launch timing of the attention kernel
+    bool profiling = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
+    size_t prof_used = 0;
+
+    // host-buffer entry point staging
+    void *h_in = nullptr, *h_out = nullptr, *d_kv = nullptr, *d_q = nullptr, *d_out = nullptr;
+};
+
+namespace {
+
+int fail(mla_ctx* c, int code, std::string msg)
+{
+    if (c) c->err = std::move(msg);
+    else g_create_error = std::move(msg);
+    return code;
+}
+
+#define CU_TRY(c, expr)                                                                           \
+    do {                                                                                          \
+        cudaError_t e__ = (expr);                                                                 \
+        if (e__ != cudaSuccess)                                                                   \
+            return fail((c), MLA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+int pt_code(mla_ctx* c, int e)
+{
+    if (e == mugen::mla::PT_OK) return MLA_OK;
+    c->err = c->pt->error();
+    return e;   // PT_* values equal the MLA_ERR_* values they stand for
+}
+
+size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
+
+inline float half_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+inline uint16_t f32_to_half_bits(float f) { return __half_as_ushort(__float2half_rn(f)); }
+inline uint16_t f32_to_bf16_bits(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+
+// Decodes (n_rows x 512) weights of GGML type `w_type` into the context storage dtype.
+int decode_weights(mla_ctx* c, const void* w, uint32_t w_type, size_t n_rows, std::vector<uint16_t>& out)
+{
+    const size_t n = n_rows * mla::kRank;
+    out.resize(n);
+    const bool to_half = c->cfg.dtype == MLA_DTYPE_F16;
+    auto put = [&](size_t i, float v) { out[i] = to_half ? f32_to_half_bits(v) : f32_to_bf16_bits(v); };
+    if (w_type == MLA_W_F16) {
+        const auto* s = static_cast<const uint16_t*>(w);
+        if (to_half) std::memcpy(out.data(), s, n * 2);
+        else for (size_t i = 0; i < n; i++) put(i, half_bits_to_f32(s[i]));
+    } else if (w_type == MLA_W_BF16) {
+        const auto* s = static_cast<const uint16_t*>(w);
+        if (!to_half) std::memcpy(out.data(), s, n * 2);
+        else for (size_t i = 0; i < n; i++) {
+            const uint32_t u = uint32_t(s[i]) << 16;
+            float f;
+            std::memcpy(&f, &u, 4);
+            put(i, f);
+        }
+    } else if (w_type == MLA_W_Q8_0) {
+        const auto* s = static_cast<const uint8_t*>(w);
+        const size_t nb = n / 32;
+        for (size_t b = 0; b < nb; b++) {
+            const uint8_t* blk = s + b * 34;
+            uint16_t d;
+            std::memcpy(&d, blk, 2);
+            const float sc = half_bits_to_f32(d);
+            for (int j = 0; j < 32; j++) put(b * 32 + j, sc * float(int8_t(blk[2 + j])));
+        }
+    } else if (w_type == MLA_W_Q4_0) {
+        const auto* s = static_cast<const uint8_t*>(w);
+        const size_t nb = n / 32;
+        for (size_t b = 0; b < nb; b++) {
+            const uint8_t* blk = s + b * 18;
+            uint16_t d;
+            std::memcpy(&d, blk, 2);
+            const float sc = half_bits_to_f32(d);
+            for (int j = 0; j < 16; j++) {
+                put(b * 32 + j, float(int(blk[2 + j] & 0x0F) - 8) * sc);
+                put(b * 32 + j + 16, float(int(blk[2 + j] >> 4) - 8) * sc);
+            }
+        }
+    } else {
+        return fail(c, MLA_ERR_UNSUPPORTED, "weight type " + std::to_string(w_type) +
+                                                " is not one of F16, BF16, Q8_0, Q4_0");
+    }
+    return MLA_OK;
+}
+
+int ensure_rope_rows(mla_ctx* c, uint32_t upto, cudaStream_t st)
+{
+    if (upto <= c->cs_rows) return MLA_OK;
+    if (upto > c->cs_cap)
+        return fail(c, MLA_ERR_CAPACITY, "position " + std::to_string(upto - 1) +
+                                             " beyond the rotary table capacity " + std::to_string(c->cs_cap));
+    // grow in chunks so that a decode loop does not upload one row per step
+    uint32_t target = std::min<uint32_t>(c->cs_cap, std::max<uint32_t>(upto, c->cs_rows + 4096));
+    std::vector<float> rows(size_t(target - c->cs_rows) * mla::kRope);
+    mugen::mla::fill_rope_rows(rows.data(), c->cs_rows, target, c->cfg.rope_scaling_factor,
+                               c->cfg.rope_original_ctx, c->cfg.rope_theta);
+    CU_TRY(c, cudaMemcpyAsync(c->cos_sin + size_t(c->cs_rows) * mla::kRope, rows.data(),
+                              rows.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+    CU_TRY(c, cudaStreamSynchronize(st));   // `rows` is pageable and about to go away
+    c->cs_rows = target;
+    return MLA_OK;
+}
+
+struct RowSpec {
+    uint32_t seq_index;   // index into the step's sequence list
+    uint32_t attend_len;  // rows attended (0 allowed)
+    uint32_t pos;         // global position of the appended token (append only)
+    uint64_t slot;        // destination slot (append only)
+};
+
+// Packs the step metadata, uploads it through the pinned ring and points c->meta at it.
+int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vector<RowSpec>& rows,
+                bool with_segments, cudaStream_t st)
+{
+    const uint32_t R = uint32_t(rows.size()), S = uint32_t(seq_ids.size());
+    std::vector<uint32_t> lens(R);
+    for (uint32_t r = 0; r < R; r++) lens[r] = rows[r].attend_len;
+    std::vector<Segment> segs;
+    std::vector<uint32_t> row_seg_begin, cta_seg_begin;
+    if (with_segments) {
+        mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin);
+        if (segs.size() > c->max_segs)
+            return fail(c, MLA_ERR_CAPACITY, "step needs " + std::to_string(segs.size()) +
+                                                 " KV segments, workspace holds " + std::to_string(c->max_segs));
+    } else {
+        row_seg_begin.assign(R + 1, 0);
+        cta_seg_begin.assign(1, 0);
+    }
+    const uint32_t G = uint32_t(segs.size()), W = uint32_t(cta_seg_begin.size()) - 1;
+    size_t tbl_total = 0;
+    std::vector<uint32_t> tbl_off(S);
+    for (uint32_t i = 0; i < S; i++) {
+        tbl_off[i] = uint32_t(tbl_total);
+        tbl_total += c->pt->seq(seq_ids[i])->pages.size();
+    }
+    // layout
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align16(off + bytes); return o; };
+    const size_t o_slot = take(size_t(R) * 8), o_seq = take(size_t(R) * 4), o_len = take(size_t(R) * 4),
+                 o_pos = take(size_t(R) * 4), o_tblo = take(size_t(S) * 4), o_tbl = take(tbl_total * 4 + 4),
+                 o_sr = take(size_t(G) * 4), o_sb = take(size_t(G) * 4), o_se = take(size_t(G) * 4),
+                 o_rsb = take(size_t(R + 1) * 4), o_csb = take(size_t(W + 1) * 4);
+    if (off > c->meta_cap)
+        return fail(c, MLA_ERR_CAPACITY, "step metadata (" + std::to_string(off) + " B) exceeds the buffer (" +
+                                             std::to_string(c->meta_cap) + " B)");
+    MetaBuf& mb = c->ring[c->ring_next];
+    c->ring_next = (c->ring_next + 1) % kMetaRing;
+    if (mb.in_flight) {
+        CU_TRY(c, cudaEventSynchronize(mb.done));
+        mb.in_flight = false;
+    }
+    char* h = static_cast<char*>(mb.host);
+    auto* p_slot = reinterpret_cast<uint64_t*>(h + o_slot);
+    auto* p_seq = reinterpret_cast<uint32_t*>(h + o_seq);
+    auto* p_len = reinterpret_cast<uint32_t*>(h + o_len);
+    auto* p_pos = reinterpret_cast<uint32_t*>(h + o_pos);
+    for (uint32_t r = 0; r < R; r++) {
+        p_slot[r] = rows[r].slot;
+        p_seq[r] = rows[r].seq_index;
+        p_len[r] = rows[r].attend_len;
+        p_pos[r] = rows[r].pos;
+    }
+    std::memcpy(h + o_tblo, tbl_off.data(), size_t(S) * 4);
+    auto* p_tbl = reinterpret_cast<uint32_t*>(h + o_tbl);
+    for (uint32_t i = 0; i < S; i++) {
+        const auto& pg = c->pt->seq(seq_ids[i])->pages;
+        std::memcpy(p_tbl + tbl_off[i], pg.data(), pg.size() * 4);
+    }
+    auto* p_sr = reinterpret_cast<uint32_t*>(h + o_sr);
+    auto* p_sb = reinterpret_cast<uint32_t*>(h + o_sb);
+    auto* p_se = reinterpret_cast<uint32_t*>(h + o_se);
+    for (uint32_t g = 0; g < G; g++) {
+        p_sr[g] = segs[g].row;
+        p_sb[g] = segs[g].page_begin;
+        p_se[g] = segs[g].page_end;
+    }
+    std::memcpy(h + o_rsb, row_seg_begin.data(), size_t(R + 1) * 4);
+    std::memcpy(h + o_csb, cta_seg_begin.data(), size_t(W + 1) * 4);
+    if (off) CU_TRY(c, cudaMemcpyAsync(c->meta_dev, h, off, cudaMemcpyHostToDevice, st));
+    CU_TRY(c, cudaEventRecord(mb.done, st));
+    mb.in_flight = true;
+
+    char* d = c->meta_dev;
+    mla::StepMeta& m = c->meta;
+    m.row_slot = reinterpret_cast<const uint64_t*>(d + o_slot);
+    m.row_seq = reinterpret_cast<const uint32_t*>(d + o_seq);
+    m.row_len = reinterpret_cast<const uint32_t*>(d + o_len);
+    m.row_pos = reinterpret_cast<const uint32_t*>(d + o_pos);
+    m.seq_tbl_off = reinterpret_cast<const uint32_t*>(d + o_tblo);
+    m.tables = reinterpret_cast<const uint32_t*>(d + o_tbl);
+    m.seg_row = reinterpret_cast<const uint32_t*>(d + o_sr);
+    m.seg_page_begin = reinterpret_cast<const uint32_t*>(d + o_sb);
+    m.seg_page_end = reinterpret_cast<const uint32_t*>(d + o_se);
+    m.row_seg_begin = reinterpret_cast<const uint32_t*>(d + o_rsb);
+    m.cta_seg_begin = reinterpret_cast<const uint32_t*>(d + o_csb);
+    m.rows = R;
+    m.segs = G;
+    m.ctas = W;
+    return MLA_OK;
+}
+
+char* layer_pool(mla_ctx* c, uint32_t layer)
+{
+    return c->pool + size_t(layer) * c->pool_slots * mla::kRow * 2;
+}
+
+int check_layer(mla_ctx* c, uint32_t layer, bool need_weights)
+{
+    if (layer >= c->cfg.n_layers) return fail(c, MLA_ERR_INVALID, "layer " + std::to_string(layer) + " out of range");
+    if (need_weights && !c->layers[layer].set)
+        return fail(c, MLA_ERR_STATE, "weights of layer " + std::to_string(layer) + " were never registered");
+    return MLA_OK;
+}
+
+int run_append(mla_ctx* c, uint32_t layer, const void* kv_a, cudaStream_t st)
+{
+    mla::launch_append(int(c->cfg.dtype), kv_a, layer_pool(c, layer), c->pool_slots, c->layers[layer].norm,
+                       c->cos_sin, c->cs_rows, c->cfg.rms_norm_eps, c->meta, c->status_dev, st);
+    c->launches += c->meta.rows ? 1 : 0;
+    CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+// absorb -> split-KV attention -> merge (+ W_UV, or export of the merged partial state)
+int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st)
+{
+    const mla::StepMeta& m = c->meta;
+    if (m.rows == 0) return MLA_OK;
+    const uint32_t H = c->cfg.n_heads;
+    mla::launch_absorb(int(c->cfg.dtype), q, c->layers[layer].w_uk, c->q_abs, m.rows, H, st);
+    int e;
+    const bool timed = c->profiling && c->prof_used < c->prof_events.size();
+    if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
+    if (c->kernel == MLA_KERNEL_TCGEN05)
+        e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmap_dev, layer, c->cfg.n_pages, m,
+                                   c->recs, H, c->status_dev, st);
+    else
+        e = mla::launch_decode_mma(int(c->cfg.dtype), c->q_abs, layer_pool(c, layer), c->cfg.n_pages, m,
+                                   c->recs, H, c->status_dev, st);
+    if (e != 0) return fail(c, MLA_ERR_CUDA, std::string("attention launch: ") + cudaGetErrorString(cudaError_t(e)));
+    if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used++].second, st));
+    mla::launch_merge(int(c->cfg.dtype), c->recs, m.row_seg_begin, 0, c->layers[layer].w_uv, out, exported,
+                      m.rows, H, st);
+    c->launches += 3;
+    CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+int make_tensor_map(mla_ctx* c)
+{
+    // cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda.
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CU_TRY(c, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+        return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap tm;
+    // dims innermost first: 576 values, token slots of a layer, layers
+    const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
+    const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
+    const cuuint32_t box[3] = {64, 64, 1};      // 64 values (128 B) x 64 tokens: one swizzled sub-tile
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = c->cfg.dtype == MLA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = reinterpret_cast<EncodeFn>(fn)(&tm, dt, 3, c->pool, dims, strides, box, estr,
+                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    CU_TRY(c, cudaMalloc(&c->tmap_dev, sizeof(CUtensorMap)));
+    CU_TRY(c, cudaMemcpy(c->tmap_dev, &tm, sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+    return MLA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mla_create(const mla_config* cfg, mla_ctx** out)
+{
+    if (!cfg || !out) return fail(nullptr, MLA_ERR_INVALID, "null argument");
+    *out = nullptr;
+    // same wording as KVCache::create's validation (src/core/memory/kv_cache.cpp:146-159)
+    if (cfg->n_layers == 0) return fail(nullptr, MLA_ERR_INVALID, "n_layers must be > 0");
+    if (cfg->n_heads == 0) return fail(nullptr, MLA_ERR_INVALID, "n_heads must be > 0");
+    if (cfg->max_seq_len == 0) return fail(nullptr, MLA_ERR_INVALID, "max_seq_len must be > 0");
+    if (cfg->kv_lora_rank != 512 || cfg->qk_nope_head_dim != 128 || cfg->qk_rope_head_dim != 64 ||
+        cfg->v_head_dim != 128)
+        return fail(nullptr, MLA_ERR_UNSUPPORTED,
+                    "only kv_lora_rank 512, qk_nope_head_dim 128, qk_rope_head_dim 64, v_head_dim 128 are built");
+    if (cfg->page_tokens != 64) return fail(nullptr, MLA_ERR_UNSUPPORTED, "page_tokens must be 64");
+    if (cfg->n_pages == 0 || cfg->max_seqs == 0) return fail(nullptr, MLA_ERR_INVALID, "n_pages and max_seqs must be > 0");
+    if (cfg->dtype > MLA_DTYPE_BF16) return fail(nullptr, MLA_ERR_INVALID, "dtype must be MLA_DTYPE_F16 or MLA_DTYPE_BF16");
+    if (cfg->kernel > MLA_KERNEL_TCGEN05) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
+
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        return fail(nullptr, MLA_ERR_CUDA, std::string("no CUDA device: ") + cudaGetErrorString(e) +
+                                               " (this library has no CPU path)");
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, MLA_ERR_INVALID, "device ordinal out of range");
+
+    auto c = std::make_unique<mla_ctx>();
+    c->cfg = *cfg;
+    if (c->cfg.max_rows == 0) c->cfg.max_rows = c->cfg.max_seqs;
+    mla_ctx* cp = c.get();
+    auto bail = [&](int code) { g_create_error = cp->err; mla_destroy(c.release()); return code; };
+#define CR_TRY(expr)                                                                            \
+    do {                                                                                        \
+        cudaError_t e__ = (expr);                                                               \
+        if (e__ != cudaSuccess) {                                                               \
+            cp->err = std::string(#expr) + ": " + cudaGetErrorString(e__);                     \
+            return bail(MLA_ERR_CUDA);                                                          \
+        }                                                                                       \
+    } while (0)
+    CR_TRY(cudaSetDevice(cfg->device));
+    cudaDeviceProp prop{};
+    CR_TRY(cudaGetDeviceProperties(&prop, cfg->device));
+    c->sm_count = prop.multiProcessorCount;
+    if (prop.major != 10)
+        { cp->err = "this library is built for sm_100a only; device is sm_" + std::to_string(prop.major * 10 + prop.minor);
+          return bail(MLA_ERR_UNSUPPORTED); }
+    c->kernel = cfg->kernel == MLA_KERNEL_AUTO ? MLA_KERNEL_MMA : cfg->kernel;
+    const uint32_t H = cfg->n_heads;
+    if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
+    else c->workers = std::max<uint32_t>(1, c->sm_count * 2 / ((H + 15) / 16));
+
+    c->pt = std::make_unique<PageTable>(cfg->page_tokens, cfg->n_pages, cfg->max_seqs, cfg->max_seq_len);
+    c->layers.resize(cfg->n_layers);
+    c->pool_slots = uint64_t(cfg->n_pages) * cfg->page_tokens;
+    const size_t pool_bytes = size_t(cfg->n_layers) * c->pool_slots * mla::kRow * 2;
+    CR_TRY(cudaMalloc(&c->pool, pool_bytes));
+    // zero-fill: rows past a sequence's end inside its last page are multiplied by P = 0 and
+    // must therefore hold finite values
+    CR_TRY(cudaMemset(c->pool, 0, pool_bytes));
+    for (auto& lw : c->layers) {
+        CR_TRY(cudaMalloc(&lw.w_uk, size_t(H) * mla::kNope * mla::kRank * 2));
+        CR_TRY(cudaMalloc(&lw.w_uv, size_t(H) * mla::kVDim * mla::kRank * 2));
+        CR_TRY(cudaMalloc(&lw.norm, mla::kRank * 2));
+    }
+    // rotary table: one row per position a sequence can reach
+    c->cs_cap = std::max(cfg->max_seq_len, cfg->max_position);
+    CR_TRY(cudaMalloc(&c->cos_sin, size_t(c->cs_cap) * mla::kRope * sizeof(float)));
+    const uint32_t R = c->cfg.max_rows;
+    CR_TRY(cudaMalloc(&c->q_abs, size_t(R) * H * mla::kRow * 2));
+    c->max_segs = c->workers + R;
+    CR_TRY(cudaMalloc(&c->recs, size_t(c->max_segs) * H * mla::kPart * sizeof(float)));
+    CR_TRY(cudaMalloc(&c->status_dev, sizeof(uint32_t)));
+    CR_TRY(cudaMemset(c->status_dev, 0, sizeof(uint32_t)));
+    const size_t max_pages_per_seq = (size_t(cfg->max_seq_len) + cfg->page_tokens - 1) / cfg->page_tokens;
+    const size_t tbl_entries = std::min<size_t>(size_t(cfg->max_seqs) * max_pages_per_seq, cfg->n_pages) + 4;
+    c->meta_cap = align16(size_t(R) * 8) + 3 * align16(size_t(R) * 4) + align16(size_t(cfg->max_seqs) * 4) +
+                  align16(tbl_entries * 4 + 4) + 3 * align16(size_t(c->max_segs) * 4) +
+                  align16(size_t(R + 1) * 4) + align16(size_t(c->workers + 1) * 4) + 256;
+    CR_TRY(cudaMalloc(&c->meta_dev, c->meta_cap));
+    for (auto& mb : c->ring) {
+        CR_TRY(cudaMallocHost(&mb.host, c->meta_cap));
+        CR_TRY(cudaEventCreateWithFlags(&mb.done, cudaEventDisableTiming));
+    }
+    if (c->kernel == MLA_KERNEL_TCGEN05) {
+        if (int rc = make_tensor_map(cp)) return bail(rc);
+        if (int ce = mla::decode_tc5_configure()) {
+            cp->err = std::string("tcgen05 kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+            return bail(MLA_ERR_CUDA);
+        }
+    }
+#undef CR_TRY
+    *out = c.release();
+    return MLA_OK;
+}
+
+void mla_destroy(mla_ctx* c)
+{
+    if (!c) return;
+    cudaSetDevice(c->cfg.device);
+    cudaDeviceSynchronize();
+    cudaFree(c->pool);
+    for (auto& lw : c->layers) { cudaFree(lw.w_uk); cudaFree(lw.w_uv); cudaFree(lw.norm); }
+    cudaFree(c->cos_sin);
+    cudaFree(c->q_abs);
+    cudaFree(c->recs);
+    cudaFree(c->status_dev);
+    cudaFree(c->tmap_dev);
+    cudaFree(c->meta_dev);
+    for (auto& mb : c->ring) {
+        if (mb.host) cudaFreeHost(mb.host);
+        if (mb.done) cudaEventDestroy(mb.done);
+    }
+    for (auto& pe : c->prof_events) { cudaEventDestroy(pe.first); cudaEventDestroy(pe.second); }
+    if (c->h_in) cudaFreeHost(c->h_in);
+    if (c->h_out) cudaFreeHost(c->h_out);
+    cudaFree(c->d_kv); cudaFree(c->d_q); cudaFree(c->d_out);
+    delete c;
+}
+
+const char* mla_last_error(const mla_ctx* c) { return c ? c->err.c_str() : g_create_error.c_str(); }
+
+int mla_status(mla_ctx* c, void* stream, uint32_t* device_status)
+{
+    if (!c || !device_status) return MLA_ERR_INVALID;
+    auto st = static_cast<cudaStream_t>(stream);
+    uint32_t v = 0;
+    CU_TRY(c, cudaMemcpyAsync(&v, c->status_dev, 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(c, cudaStreamSynchronize(st));
+    if (v) CU_TRY(c, cudaMemsetAsync(c->status_dev, 0, 4, st));
+    *device_status = v;
+    if (v) return fail(c, MLA_ERR_DEVICE, "device status word = " + std::to_string(v));
+    return MLA_OK;
+}
+
+int mla_set_layer_weights(mla_ctx* c, uint32_t layer, const void* w_uk, const void* w_uv, uint32_t w_type,
+                          const void* kv_norm)
+{
+    if (!c || !w_uk || !w_uv || !kv_norm) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, false)) return e;
+    CU_TRY(c, cudaSetDevice(c->cfg.device));
+    std::vector<uint16_t> buf;
+    const size_t H = c->cfg.n_heads;
+    if (int e = decode_weights(c, w_uk, w_type, H * mla::kNope, buf)) return e;
+    CU_TRY(c, cudaMemcpy(c->layers[layer].w_uk, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
+    if (int e = decode_weights(c, w_uv, w_type, H * mla::kVDim, buf)) return e;
+    CU_TRY(c, cudaMemcpy(c->layers[layer].w_uv, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
+    CU_TRY(c, cudaMemcpy(c->layers[layer].norm, kv_norm, mla::kRank * 2, cudaMemcpyHostToDevice));
+    c->layers[layer].set = true;
+    return MLA_OK;
+}
+
+int mla_seq_create(mla_ctx* c, uint32_t* id)
+{
+    if (!c || !id) return MLA_ERR_INVALID;
+    return pt_code(c, c->pt->seq_create(id));
+}
+int mla_seq_free(mla_ctx* c, uint32_t id) { return c ? pt_code(c, c->pt->seq_free(id)) : MLA_ERR_INVALID; }
+int mla_seq_len(const mla_ctx* c, uint32_t id, uint32_t* len)
+{
+    if (!c || !len) return MLA_ERR_INVALID;
+    return c->pt->seq_len(id, len);
+}
+int mla_advance(mla_ctx* c, uint32_t id, uint32_t n) { return c ? pt_code(c, c->pt->advance(id, n)) : MLA_ERR_INVALID; }
+int mla_truncate(mla_ctx* c, uint32_t id, uint32_t n) { return c ? pt_code(c, c->pt->truncate(id, n)) : MLA_ERR_INVALID; }
+int mla_clear(mla_ctx* c, uint32_t id) { return c ? pt_code(c, c->pt->clear(id)) : MLA_ERR_INVALID; }
+int mla_seq_set_base(mla_ctx* c, uint32_t id, uint32_t base) { return c ? pt_code(c, c->pt->set_base(id, base)) : MLA_ERR_INVALID; }
+int mla_free_pages(const mla_ctx* c, uint32_t* n)
+{
+    if (!c || !n) return MLA_ERR_INVALID;
+    *n = c->pt->free_pages();
+    return MLA_OK;
+}
+int mla_shuffle_free_pages(mla_ctx* c, uint64_t seed)
+{
+    if (!c) return MLA_ERR_INVALID;
+    c->pt->shuffle_free(seed);
+    return MLA_OK;
+}
+int mla_seq_pages(const mla_ctx* c, uint32_t id, uint32_t* pages, uint32_t cap, uint32_t* n_pages)
+{
+    if (!c || !n_pages) return MLA_ERR_INVALID;
+    const auto* s = c->pt->seq(id);
+    if (!s) return MLA_ERR_INVALID;
+    *n_pages = uint32_t(s->pages.size());
+    if (pages) std::memcpy(pages, s->pages.data(), std::min<size_t>(cap, s->pages.size()) * 4);
+    return MLA_OK;
+}
+
+int mla_append_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_ids, const uint32_t* positions,
+                    const void* kv_a, void* stream)
+{
+    if (!c || (n && (!seq_ids || !positions || !kv_a))) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, true)) return e;
+    if (c->in_step) return fail(c, MLA_ERR_STATE, "explicit-position calls are not allowed while a step is open");
+    if (n > c->cfg.max_rows) return fail(c, MLA_ERR_CAPACITY, "more rows than max_rows");
+    auto st = static_cast<cudaStream_t>(stream);
+    std::vector<uint32_t> seqs;
+    std::vector<RowSpec> rows(n);
+    uint32_t max_pos = 0;
+    for (uint32_t r = 0; r < n; r++) {
+        const auto* s = c->pt->seq(seq_ids[r]);
+        if (!s) return fail(c, MLA_ERR_INVALID, "unknown sequence id " + std::to_string(seq_ids[r]));
+        if (positions[r] < s->base_pos) return fail(c, MLA_ERR_INVALID, "position below the sequence's base position");
+        const uint32_t local = positions[r] - s->base_pos;
+        if (int e = pt_code(c, c->pt->reserve(seq_ids[r], local + 1))) return e;
+        rows[r] = {0, 0, positions[r], c->pt->slot(seq_ids[r], local)};
+        max_pos = std::max(max_pos, positions[r]);
+    }
+    if (n) if (int e = ensure_rope_rows(c, max_pos + 1, st)) return e;
+    if (int e = upload_meta(c, seqs, rows, false, st)) return e;
+    return run_append(c, layer, kv_a, st);
+}
+
+int mla_attend_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_ids, const uint32_t* attend_lens,
+                    const void* q, void* out, void* stream)
+{
+    if (!c || (n && (!seq_ids || !attend_lens || !q || !out))) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, true)) return e;
+    if (c->in_step) return fail(c, MLA_ERR_STATE, "explicit-position calls are not allowed while a step is open");
+    if (n > c->cfg.max_rows) return fail(c, MLA_ERR_CAPACITY, "more rows than max_rows");
+    auto st = static_cast<cudaStream_t>(stream);
+    std::vector<uint32_t> seqs;
+    std::vector<RowSpec> rows(n);
+    for (uint32_t r = 0; r < n; r++) {
+        const auto* s = c->pt->seq(seq_ids[r]);
+        if (!s) return fail(c, MLA_ERR_INVALID, "unknown sequence id " + std::to_string(seq_ids[r]));
+        if (uint64_t(attend_lens[r]) > uint64_t(s->pages.size()) * mla::kPage)
+            return fail(c, MLA_ERR_INVALID, "attend length " + std::to_string(attend_lens[r]) +
+                                                " reaches rows that were never appended");
+        uint32_t idx = 0;
+        for (; idx < seqs.size(); idx++) if (seqs[idx] == seq_ids[r]) break;
+        if (idx == seqs.size()) seqs.push_back(seq_ids[r]);
+        rows[r] = {idx, attend_lens[r], 0, 0};
+    }
+    if (int e = upload_meta(c, seqs, rows, true, st)) return e;
+    return run_attend(c, layer, q, out, nullptr, st);
+}
+
+int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const uint32_t* n_new, void* stream)
+{
+    if (!c || (n_seq && !seq_ids)) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (c->in_step) return fail(c, MLA_ERR_STATE, "step_begin while a step is open");
+    auto st = static_cast<cudaStream_t>(stream);
+    std::vector<uint32_t> seqs(seq_ids, seq_ids + n_seq);
+    std::vector<uint32_t> nn(n_seq, 1);
+    if (n_new) nn.assign(n_new, n_new + n_seq);
+    uint64_t total = 0;
+    for (uint32_t i = 0; i < n_seq; i++) {
+        if (!c->pt->seq(seqs[i])) return fail(c, MLA_ERR_INVALID, "unknown sequence id " + std::to_string(seqs[i]));
+        for (uint32_t j = 0; j < i; j++)
+            if (seqs[j] == seqs[i]) return fail(c, MLA_ERR_INVALID, "sequence listed twice in one step");
+        total += std::max<uint32_t>(nn[i], 1);
+    }
+    if (total > c->cfg.max_rows) return fail(c, MLA_ERR_CAPACITY, "step has " + std::to_string(total) + " rows, max_rows is " + std::to_string(c->cfg.max_rows));
+    // reserve first (all-or-nothing per sequence; on failure earlier reservations stay, harmless)
+    uint32_t max_pos = 0;
+    for (uint32_t i = 0; i < n_seq; i++) {
+        const auto* s = c->pt->seq(seqs[i]);
+        if (int e = pt_code(c, c->pt->reserve(seqs[i], s->len + nn[i]))) return e;
+        if (nn[i]) max_pos = std::max(max_pos, s->base_pos + s->len + nn[i] - 1);
+    }
+    if (total) if (int e = ensure_rope_rows(c, max_pos + 1, st)) return e;
+    std::vector<RowSpec> rows;
+    rows.reserve(total);
+    for (uint32_t i = 0; i < n_seq; i++) {
+        const auto* s = c->pt->seq(seqs[i]);
+        if (nn[i] == 0) rows.push_back({i, s->len, 0, ~uint64_t(0)});   // query-only row
+        for (uint32_t t = 0; t < nn[i]; t++) {
+            const uint32_t local = s->len + t;
+            rows.push_back({i, local + 1, s->base_pos + local, c->pt->slot(seqs[i], local)});
+        }
+    }
+    if (int e = upload_meta(c, seqs, rows, true, st)) return e;
+    c->step_seqs = std::move(seqs);
+    c->step_nnew = std::move(nn);
+    c->in_step = true;
+    return MLA_OK;
+}
+
+int mla_step_append(mla_ctx* c, uint32_t layer, const void* kv_a, void* stream)
+{
+    if (!c || !kv_a) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_append outside step_begin/step_end");
+    if (int e = check_layer(c, layer, true)) return e;
+    return run_append(c, layer, kv_a, static_cast<cudaStream_t>(stream));
+}
+
+int mla_step_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, void* stream)
+{
+    if (!c || !q || !out) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_attend outside step_begin/step_end");
+    if (int e = check_layer(c, layer, true)) return e;
+    return run_attend(c, layer, q, out, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int mla_step_attend_partial(mla_ctx* c, uint32_t layer, const void* q, float* partial, void* stream)
+{
+    if (!c || !q || !partial) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_attend_partial outside step_begin/step_end");
+    if (int e = check_layer(c, layer, true)) return e;
+    return run_attend(c, layer, q, nullptr, partial, static_cast<cudaStream_t>(stream));
+}
+
+int mla_merge_partials(mla_ctx* c, uint32_t layer, uint32_t n_parts, uint32_t rows, const float* partials,
+                       void* out, void* stream)
+{
+    if (!c || !partials || !out || n_parts == 0) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, true)) return e;
+    mla::launch_merge(int(c->cfg.dtype), partials, nullptr, n_parts, c->layers[layer].w_uv, out, nullptr, rows,
+                      c->cfg.n_heads, static_cast<cudaStream_t>(stream));
+    c->launches += rows ? 1 : 0;
+    CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const void* q_host, void* out_host,
+                        void* stream)
+{
+    if (!c || !kv_a_host || !q_host || !out_host) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layer_host outside step_begin/step_end");
+    if (int e = check_layer(c, layer, true)) return e;
+    auto st = static_cast<cudaStream_t>(stream);
+    const size_t R = c->cfg.max_rows, H = c->cfg.n_heads, rows = c->meta.rows;
+    const size_t kv_b = rows * mla::kRow * 2, q_b = rows * H * mla::kQDim * 2, o_b = rows * H * mla::kVDim * 2;
+    if (!c->h_in) {
+        CU_TRY(c, cudaMallocHost(&c->h_in, R * mla::kRow * 2 + R * H * mla::kQDim * 2));
+        CU_TRY(c, cudaMallocHost(&c->h_out, R * H * mla::kVDim * 2));
+        CU_TRY(c, cudaMalloc(&c->d_kv, R * mla::kRow * 2));
+        CU_TRY(c, cudaMalloc(&c->d_q, R * H * mla::kQDim * 2));
+        CU_TRY(c, cudaMalloc(&c->d_out, R * H * mla::kVDim * 2));
+    }
+    // the staging buffers are reused by the next call: drain the stream's earlier use of them
+    CU_TRY(c, cudaStreamSynchronize(st));
+    std::memcpy(c->h_in, kv_a_host, kv_b);
+    std::memcpy(static_cast<char*>(c->h_in) + R * mla::kRow * 2, q_host, q_b);
+    CU_TRY(c, cudaMemcpyAsync(c->d_kv, c->h_in, kv_b, cudaMemcpyHostToDevice, st));
+    CU_TRY(c, cudaMemcpyAsync(c->d_q, static_cast<char*>(c->h_in) + R * mla::kRow * 2, q_b, cudaMemcpyHostToDevice, st));
+    if (int e = run_append(c, layer, c->d_kv, st)) return e;
+    if (int e = run_attend(c, layer, c->d_q, c->d_out, nullptr, st)) return e;
+    CU_TRY(c, cudaMemcpyAsync(c->h_out, c->d_out, o_b, cudaMemcpyDeviceToHost, st));
+    CU_TRY(c, cudaStreamSynchronize(st));
+    std::memcpy(out_host, c->h_out, o_b);
+    return MLA_OK;
+}
+
+int mla_step_end(mla_ctx* c)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_end without step_begin");
+    c->in_step = false;
+    for (size_t i = 0; i < c->step_seqs.size(); i++)
+        if (int e = pt_code(c, c->pt->advance(c->step_seqs[i], c->step_nnew[i]))) return e;
+    return MLA_OK;
+}
+
+int mla_step_info(const mla_ctx* c, uint32_t* rows, uint32_t* segments)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (rows) *rows = c->meta.rows;
+    if (segments) *segments = c->meta.segs;
+    return MLA_OK;
+}
+
+int mla_launch_count(const mla_ctx* c, uint64_t* n)
+{
+    if (!c || !n) return MLA_ERR_INVALID;
+    *n = c->launches;
+    return MLA_OK;
+}
+
+int mla_profile_enable(mla_ctx* c, int on)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (on && c->prof_events.empty()) {
+        c->prof_events.resize(8192);
+        for (auto& pe : c->prof_events) {
+            CU_TRY(c, cudaEventCreate(&pe.first));
+            CU_TRY(c, cudaEventCreate(&pe.second));
+        }
+    }
+    c->profiling = on != 0;
+    return MLA_OK;
+}
+
+int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
+{
+    if (!c || !launches || !total_ms) return MLA_ERR_INVALID;
+    float sum = 0.0f;
+    for (size_t i = 0; i < c->prof_used; i++) {
+        CU_TRY(c, cudaEventSynchronize(c->prof_events[i].second));
+        float ms = 0.0f;
+        CU_TRY(c, cudaEventElapsedTime(&ms, c->prof_events[i].first, c->prof_events[i].second));
+        sum += ms;
+    }
+    *launches = uint32_t(c->prof_used);
+    *total_ms = sum;
+    c->prof_used = 0;
+    return MLA_OK;
+}
+
+const char* mla_kernel_name(const mla_ctx* c)
+{
+    if (!c) return "";
+    return c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
+}
+
+int mla_read_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, void* host_out, void* stream)
+{
+    if (!c || !host_out) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, false)) return e;
+    const auto* s = c->pt->seq(id);
+    if (!s) return fail(c, MLA_ERR_INVALID, "unknown sequence id");
+    if (uint64_t(row_begin) + n > uint64_t(s->pages.size()) * mla::kPage)
+        return fail(c, MLA_ERR_INVALID, "rows were never appended");
+    auto st = static_cast<cudaStream_t>(stream);
+    const size_t rb = mla::kRow * 2;
+    for (uint32_t r = 0; r < n;) {   // one copy per page run
+        const uint32_t row = row_begin + r;
+        const uint32_t in_page = std::min<uint32_t>(n - r, mla::kPage - row % mla::kPage);
+        CU_TRY(c, cudaMemcpyAsync(static_cast<char*>(host_out) + size_t(r) * rb,
+                                  layer_pool(c, layer) + c->pt->slot(id, row) * rb, size_t(in_page) * rb,
+                                  cudaMemcpyDeviceToHost, st));
+        r += in_page;
+    }
+    CU_TRY(c, cudaStreamSynchronize(st));
+    return MLA_OK;
+}
+
+int mla_write_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, const void* dev_rows,
+                   void* stream)
+{
+    if (!c || (n && !dev_rows)) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (int e = check_layer(c, layer, false)) return e;
+    if (!c->pt->seq(id)) return fail(c, MLA_ERR_INVALID, "unknown sequence id");
+    if (c->in_step) return fail(c, MLA_ERR_STATE, "write_rows is not allowed while a step is open");
+    if (int e = pt_code(c, c->pt->reserve(id, row_begin + n))) return e;
+    auto st = static_cast<cudaStream_t>(stream);
+    std::vector<uint32_t> seqs{id};
+    std::vector<RowSpec> none;
+    if (int e = upload_meta(c, seqs, none, false, st)) return e;
+    mla::launch_write_rows(dev_rows, layer_pool(c, layer), c->pool_slots, c->meta.tables, row_begin, n,
+                           c->status_dev, st);
+    c->launches += n ? 1 : 0;
+    CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Shared definitions of the sm_100a MLA decode kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mla {
+
+constexpr int kRank  = 512;   // kv_lora_rank: width of c_kv
+constexpr int kRope  = 64;    // qk_rope_head_dim
+constexpr int kNope  = 128;   // qk_nope_head_dim
+constexpr int kVDim  = 128;   // v_head_dim
+constexpr int kRow   = kRank + kRope;   // 576 values per latent cache row
+constexpr int kQDim  = kNope + kRope;   // 192 values per head of q
+constexpr int kPage  = 64;    // tokens per page
+constexpr int kPart  = kRank + 2;       // floats per head of an exported partial (m, l, acc)
+
+// Bits of the device status word (kernels set these instead of trapping).
+enum : uint32_t {
+    ST_BAD_SLOT      = 1u << 0,   // append: destination slot outside the pool
+    ST_BAD_PAGE      = 1u << 1,   // attend: block-table entry outside the pool
+    ST_WAIT_TIMEOUT  = 1u << 2,   // a bounded mbarrier wait gave up
+    ST_BAD_SEGMENT   = 1u << 3,   // segment descriptor inconsistent
+};
+
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+    using pair = __half2;
+    static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+template <> struct Elem<__nv_bfloat16> {
+    using pair = __nv_bfloat162;
+    static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+
+// Per-step metadata resident on the device (one upload per step, shared by all layers).
+struct StepMeta {
+    // query rows
+    const uint32_t* row_seq;        // [rows]  index into the step's sequence list
+    const uint32_t* row_len;        // [rows]  rows of the sequence this query attends
+    const uint32_t* row_pos;        // [rows]  global position of the appended token (RoPE)
+    const uint64_t* row_slot;       // [rows]  destination token slot of the appended token
+    // block tables
+    const uint32_t* seq_tbl_off;    // [seqs]  offset of the sequence's block table in `tables`
+    const uint32_t* tables;         // physical page ids
+    // split-KV segments
+    const uint32_t* seg_row;        // [segs]
+    const uint32_t* seg_page_begin; // [segs]
+    const uint32_t* seg_page_end;   // [segs]
+    const uint32_t* row_seg_begin;  // [rows+1]  a row's segments are contiguous
+    const uint32_t* cta_seg_begin;  // [ctas+1]  a persistent block's segments are contiguous
+    uint32_t rows, segs, ctas;
+};
+
+}  // namespace mla

@@ -1,0 +1,36 @@
+// Host-callable launchers of the MLA kernels (internal to the library; the public surface is
+// include/mugen_mla.h).
+#pragma once
+
+#include "mla_common.cuh"
+
+namespace mla {
+
+void launch_append(int dtype, const void* kv_a, void* layer_pool, uint64_t pool_slots,
+                   const void* norm_w, const float* cos_sin, uint32_t cs_rows, float eps,
+                   const StepMeta& m, uint32_t* status, cudaStream_t st);
+
+void launch_write_rows(const void* src, void* layer_pool, uint64_t pool_slots, const uint32_t* table,
+                       uint32_t row_begin, uint32_t n, uint32_t* status, cudaStream_t st);
+
+void launch_absorb(int dtype, const void* q, const void* w_uk, void* q_abs, uint32_t rows,
+                   uint32_t H, cudaStream_t st);
+
+// Split-KV attention, legacy tensor path (mma.sync m16n8k16): grid (segments, ceil(H/16)).
+// Returns a cudaError_t-compatible code from the launch configuration.
+int launch_decode_mma(int dtype, const void* q_abs, const void* layer_pool, uint32_t n_pages,
+                      const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
+
+// Split-KV attention on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM,
+// cache tiles staged by TMA): grid (segments, ceil(H/64)).  tmap is the device-resident
+// CUtensorMap of the whole pool ([layers][slots][576]).
+int launch_decode_tc5(int dtype, const void* q_abs, const void* tmap, uint32_t layer,
+                      uint32_t n_pages, const StepMeta& m, float* recs, uint32_t H, uint32_t* status,
+                      cudaStream_t st);
+int decode_tc5_configure();   // sets the kernel's shared-memory attribute once
+
+void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
+                  const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
+                  cudaStream_t st);
+
+}  // namespace mla
