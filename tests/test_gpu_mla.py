@@ -86,7 +86,7 @@ def test_append_bit_exact(torch, oracle, dt, factor, ctx_len):
     case = synth.make_layer_case(11, 4, [1] * len(positions), dt)
     kw = dict(YARN, rope_scaling_factor=factor, rope_original_ctx=ctx_len)
     from mugen_b200.mla import MlaContext
-    ctx = MlaContext(n_layers=2, n_heads=4, dtype=dt, n_pages=len(positions) + 8, max_seqs=4,
+    ctx = MlaContext(n_layers=2, n_heads=4, dtype=dt, n_pages=640, max_seqs=4,
                      max_seq_len=40064, max_rows=len(positions), kernel=capi.KERNEL_MMA, **kw)
     for layer in range(2):
         ctx.set_layer_weights(layer, case.w_uk, case.w_uv, case.w_type, case.norm_w)
