@@ -60,7 +60,7 @@ struct mla_ctx {
     uint32_t max_segs = 0;
     uint32_t workers = 1;
     uint32_t* status_dev = nullptr;
-    void* tmap_dev = nullptr;       // CUtensorMap (128 B) for the tcgen05 path
+    alignas(64) CUtensorMap tmaps[2];   // tcgen05 path: [0] cache pool, [1] absorbed queries
 
     // metadata upload ring
     MetaBuf ring[kMetaRing];
@@ -310,7 +310,7 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     const bool timed = c->profiling && c->prof_used < c->prof_events.size();
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
     if (c->kernel == MLA_KERNEL_TCGEN05)
-        e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmap_dev, layer, c->cfg.n_pages, m,
+        e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmaps, layer, c->cfg.n_pages, m,
                                    c->recs, H, c->status_dev, st);
     else
         e = mla::launch_decode_mma(int(c->cfg.dtype), c->q_abs, layer_pool(c, layer), c->cfg.n_pages, m,
@@ -324,7 +324,7 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     return MLA_OK;
 }
 
-int make_tensor_map(mla_ctx* c)
+int make_tensor_maps(mla_ctx* c)
 {
     // cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda.
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -336,21 +336,32 @@ int make_tensor_map(mla_ctx* c)
     CU_TRY(c, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
     if (!fn || qres != cudaDriverEntryPointSuccess)
         return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    CUtensorMap tm;
-    // dims innermost first: 576 values, token slots of a layer, layers
-    const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
-    const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
-    const cuuint32_t box[3] = {64, 64, 1};      // 64 values (128 B) x 64 tokens: one swizzled sub-tile
-    const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = c->cfg.dtype == MLA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                  : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    CUresult r = reinterpret_cast<EncodeFn>(fn)(&tm, dt, 3, c->pool, dims, strides, box, estr,
-                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
-    CU_TRY(c, cudaMalloc(&c->tmap_dev, sizeof(CUtensorMap)));
-    CU_TRY(c, cudaMemcpy(c->tmap_dev, &tm, sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+    const cuuint32_t estr[3] = {1, 1, 1};
+    {   // cache pool: 576 values innermost, then the token slots of a layer, then layers;
+        // box = 64 values (128 B, one swizzle row) x 64 tokens (one page)
+        const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
+        const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
+        const cuuint32_t box[3] = {64, 64, 1};
+        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[0], dt, 3, c->pool, dims, strides, box, estr,
+                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool) failed with code " + std::to_string(int(r)));
+    }
+    {   // absorbed queries [max_rows * heads][576]; box = 64 values x 64 head rows
+        const cuuint64_t dims[2] = {cuuint64_t(mla::kRow), cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64};
+        const cuuint64_t strides[1] = {cuuint64_t(mla::kRow) * 2};
+        const cuuint32_t box[2] = {64, 64};
+        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[1], dt, 2, c->q_abs, dims, strides, box, estr,
+                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(queries) failed with code " + std::to_string(int(r)));
+    }
     return MLA_OK;
 }
 
@@ -424,7 +435,9 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     c->cs_cap = std::max(cfg->max_seq_len, cfg->max_position);
     CR_TRY(cudaMalloc(&c->cos_sin, size_t(c->cs_cap) * mla::kRope * sizeof(float)));
     const uint32_t R = c->cfg.max_rows;
-    CR_TRY(cudaMalloc(&c->q_abs, size_t(R) * H * mla::kRow * 2));
+    // 64 spare rows: the tcgen05 kernel fetches queries in boxes of 64 head rows
+    CR_TRY(cudaMalloc(&c->q_abs, (size_t(R) * H + 64) * mla::kRow * 2));
+    CR_TRY(cudaMemset(c->q_abs, 0, (size_t(R) * H + 64) * mla::kRow * 2));
     c->max_segs = c->workers + R;
     CR_TRY(cudaMalloc(&c->recs, size_t(c->max_segs) * H * mla::kPart * sizeof(float)));
     CR_TRY(cudaMalloc(&c->status_dev, sizeof(uint32_t)));
@@ -440,7 +453,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
         CR_TRY(cudaEventCreateWithFlags(&mb.done, cudaEventDisableTiming));
     }
     if (c->kernel == MLA_KERNEL_TCGEN05) {
-        if (int rc = make_tensor_map(cp)) return bail(rc);
+        if (int rc = make_tensor_maps(cp)) return bail(rc);
         if (int ce = mla::decode_tc5_configure()) {
             cp->err = std::string("tcgen05 kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
             return bail(MLA_ERR_CUDA);
@@ -462,7 +475,6 @@ void mla_destroy(mla_ctx* c)
     cudaFree(c->q_abs);
     cudaFree(c->recs);
     cudaFree(c->status_dev);
-    cudaFree(c->tmap_dev);
     cudaFree(c->meta_dev);
     for (auto& mb : c->ring) {
         if (mb.host) cudaFreeHost(mb.host);

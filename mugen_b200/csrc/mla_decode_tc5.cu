@@ -1,5 +1,523 @@
+// Split-KV absorbed MLA attention on the 5th-generation tensor cores of sm_100a:
+// tcgen05.mma with accumulators in tensor memory (TMEM), cache tiles staged by TMA.
+//
+// One persistent block per SM slot x one group of 64 heads.  A block walks its list of KV
+// segments (runs of whole pages of one query row); per 64-token page tile:
+//
+//   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims]
+//   QK       S[64 heads x 64 tok]   = Q'[64 x 576] . K^T          36 x tcgen05.mma  M=64  N=64 K=16
+//                                     A = Q' (K-major), B = cache sub-tiles (K-major)
+//   softmax  one thread per head reads its row of S from TMEM (tcgen05.ld), log2-domain online
+//            softmax with lazy rescaling (the running reference maximum moves only when a tile
+//            exceeds it by more than 2^8), writes P (bf16/f16) to shared memory
+//   PV       O^T[512 dims x 64 heads] += V^T[512 x 64 tok] . P^T   16 x tcgen05.mma M=128 N=64 K=16
+//                                     A = the SAME cache sub-tiles read MN-major (no second copy,
+//                                     no transpose), B = P (K-major)
+//
+// The transposed PV keeps all 128 TMEM lanes busy at M=128 and leaves O^T in 256 columns
+// (4 chunks of 128 latent dims x 64 head columns), S double-buffered in 2 x 64 more.
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 = softmax,
+// correction and epilogue (warp w touches TMEM lanes 32*(w%4) .. +31).
+// Output per (segment, head): m (reference maximum, log2 domain), l, acc[512] — 514 floats.
+//
+// Every mbarrier wait is bounded: after ~2 s a waiter raises ST_WAIT_TIMEOUT in the status word,
+// sets the block's abort flag and every role leaves its loops; TMEM is freed on all paths.
+#include <cuda.h>
+
 #include "mla_launch.h"
+
 namespace mla {
-int decode_tc5_configure() { return int(cudaErrorNotSupported); }
-int launch_decode_tc5(int, const void*, const void*, uint32_t, uint32_t, const StepMeta&, float*, uint32_t, uint32_t*, cudaStream_t) { return int(cudaErrorNotSupported); }
+
+namespace {
+
+constexpr int TILE = 64;                          // tokens per tile = one page
+constexpr int HG = 64;                            // heads per block
+constexpr int NSUB = kRow / 64;                   // 9 sub-tiles of 64 dims
+constexpr int SUB_BYTES = TILE * 128;             // 8 KB
+constexpr int KV_STAGE_BYTES = NSUB * SUB_BYTES;  // 73,728
+constexpr int KV_STAGES = 2;
+constexpr int Q_BYTES = NSUB * HG * 128;          // 73,728
+constexpr int P_BYTES = HG * 128;                 // 8,192
+constexpr int OFF_Q = 0;
+constexpr int OFF_KV = OFF_Q + Q_BYTES;
+constexpr int OFF_P = OFF_KV + KV_STAGES * KV_STAGE_BYTES;
+constexpr int OFF_MISC = OFF_P + P_BYTES;         // barriers, alpha, tmem base, abort flag
+constexpr int MISC_BYTES = 640;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // +1024: manual 1 KB alignment
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_O = 0;                     // 4 x 64 columns
+constexpr uint32_t COL_S = 256;                   // 2 x 64 columns
+
+constexpr int NUM_THREADS = 192;
+constexpr int SOFTMAX_THREADS = 128;
+constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+// barrier slots inside the misc area (8 bytes each)
+enum { B_QFULL = 0, B_QEMPTY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL0, B_SFULL1,
+       B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY, B_OFULL, B_COUNT };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+// ---- mbarrier ------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the block is aborting (either this waiter gave up or
+// another role raised the flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---- TMA -----------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// ---- tcgen05 -------------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+//   K-major : rows of 128 B (64 elements of K), 8-row groups 1024 B apart (SBO); LBO unused.
+//   MN-major: rows of 128 B (64 elements of M/N) indexed by K, 8-row groups SBO apart,
+//             64-element M/N blocks LBO apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((addr & 0x3FFFF) >> 4);
+    d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;     // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::f16, f32 accumulate.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
+                                                  uint32_t b_mn_major) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+           ((m >> 4) << 24);
+}
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+struct SegInfo {
+    uint32_t row, page_begin, n_tiles, n_tok;
+};
+
+__device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
+    SegInfo s;
+    s.row = m.seg_row[seg];
+    s.page_begin = m.seg_page_begin[seg];
+    const uint32_t pe = m.seg_page_end[seg];
+    const uint32_t len = m.row_len[s.row];
+    const uint32_t tb = s.page_begin * kPage, te = min(len, pe * kPage);
+    s.n_tok = te > tb ? te - tb : 0;
+    s.n_tiles = (s.n_tok + TILE - 1) / TILE;
+    return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_q,
+                  uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
+                  float scale_log2, uint32_t* __restrict__ status)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* sm = smem_raw + (base - raw);
+    const uint32_t sQ = base + OFF_Q, sKV = base + OFF_KV, sP = base + OFF_P;
+    const uint32_t sBar = base + OFF_MISC;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 112);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 116);
+    float* alpha_s = reinterpret_cast<float*>(sm + OFF_MISC + 128);          // [2][64], by tile parity
+    auto bar = [&](int i) { return sBar + 8u * uint32_t(i); };
+
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t cta = blockIdx.x, h0 = blockIdx.y * HG;
+    const uint32_t seg_begin = m.cta_seg_begin[cta], seg_end = m.cta_seg_begin[cta + 1];
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(bar(B_QFULL), 1);
+        mbar_init(bar(B_QEMPTY), 1);
+        mbar_init(bar(B_KVFULL0), 1);
+        mbar_init(bar(B_KVFULL1), 1);
+        mbar_init(bar(B_KVEMPTY0), 1);
+        mbar_init(bar(B_KVEMPTY1), 1);
+        mbar_init(bar(B_SFULL0), 1);
+        mbar_init(bar(B_SFULL1), 1);
+        mbar_init(bar(B_SEMPTY0), SOFTMAX_THREADS);
+        mbar_init(bar(B_SEMPTY1), SOFTMAX_THREADS);
+        mbar_init(bar(B_PFULL), SOFTMAX_THREADS);
+        mbar_init(bar(B_PEMPTY), 1);
+        mbar_init(bar(B_OFULL), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ===================== TMA producer =====================
+        if (lane == 0) {
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                // Q' of this row's head group: 9 boxes of [64 heads][64 dims]
+                ok = mbar_wait(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
+                if (!ok) break;
+                mbar_expect_tx(bar(B_QFULL), Q_BYTES);
+                for (int j = 0; j < NSUB; j++)
+                    tma_load_2d(sQ + j * (HG * 128), &map_q, bar(B_QFULL), j * 64, int(s.row * H + h0));
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
+                for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                    const uint32_t st = t % KV_STAGES;
+                    ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+                    if (!ok) break;
+                    uint32_t page = tbl[s.page_begin + j];
+                    if (page >= n_pages) {
+                        atomicOr(status, ST_BAD_PAGE);
+                        page = 0;
+                    }
+                    mbar_expect_tx(bar(B_KVFULL0 + st), KV_STAGE_BYTES);
+                    const uint32_t dst = sKV + st * KV_STAGE_BYTES;
+                    for (int c = 0; c < NSUB; c++)
+                        tma_load_3d(dst + c * SUB_BYTES, &map_kv, bar(B_KVFULL0 + st), c * 64, int(page * kPage),
+                                    int(layer));
+                }
+                nseg++;
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 64, TILE, 0, 0);
+            constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 128, HG, 1, 0);
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            // PV of tile u (global tile counter): O^T += V^T . P^T
+            auto do_pv = [&](uint32_t u, bool first_of_seg) -> bool {
+                if (!mbar_wait(bar(B_PFULL), u & 1, abort_flag, status)) return false;
+                tc_fence_after();
+                const uint32_t kvb = sKV + (u % KV_STAGES) * KV_STAGE_BYTES;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {           // 128 latent dims per chunk = 2 sub-tiles
+#pragma unroll
+                    for (int k = 0; k < TILE / 16; k++) {
+                        const uint64_t a = smem_desc(kvb + (2 * c) * SUB_BYTES + k * 2048, SUB_BYTES, 1024);
+                        const uint64_t b = smem_desc(sP + k * 32, 16, 1024);
+                        tc_mma(tmem + COL_O + c * HG, a, b, IDESC_PV, (first_of_seg && k == 0) ? 0u : 1u);
+                    }
+                }
+                tc_commit(bar(B_KVEMPTY0 + (u % KV_STAGES)));
+                tc_commit(bar(B_PEMPTY));
+                return true;
+            };
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                    const uint32_t st = t % KV_STAGES, sb = t & 1;
+                    ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
+                         mbar_wait(bar(B_SEMPTY0 + sb), ((t >> 1) & 1) ^ 1, abort_flag, status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t kvb = sKV + st * KV_STAGE_BYTES;
+#pragma unroll
+                    for (int c = 0; c < NSUB; c++) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const uint64_t a = smem_desc(sQ + c * (HG * 128) + k * 32, 16, 1024);
+                            const uint64_t b = smem_desc(kvb + c * SUB_BYTES + k * 32, 16, 1024);
+                            tc_mma(tmem + COL_S + sb * TILE, a, b, IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
+                        }
+                    }
+                    tc_commit(bar(B_SFULL0 + sb));
+                    if (j + 1 == s.n_tiles) tc_commit(bar(B_QEMPTY));
+                    if (j > 0) ok = do_pv(t - 1, j == 1);
+                }
+                if (!ok) break;
+                ok = do_pv(t - 1, s.n_tiles == 1);
+                if (ok) tc_commit(bar(B_OFULL));
+                nseg++;
+            }
+        }
+    } else {
+        // ===================== softmax / correction / epilogue =====================
+        // The 128 threads meet at a named barrier every tile.  A failed (timed-out / aborted)
+        // wait never makes a thread leave early on its own: the failure is carried to the next
+        // barrier, OR-reduced there, and all 128 threads leave together.
+        const uint32_t q4 = warp % 4;                         // TMEM sub-partition of this warp
+        const uint32_t lane_base = (q4 * 32u) << 16;
+        const bool owner = lane < 16;                         // lanes 0-15 hold head rows of S (M=64 layout)
+        const uint32_t hl = q4 * 16 + lane;                   // head (within the group) owned by this thread
+        float m_used = -INFINITY, l_run = 0.0f;
+        uint32_t t = 0, nseg = 0;
+        bool fail = false;
+        auto wait_w = [&](uint32_t b, uint32_t parity) {      // warp-uniform bounded wait
+            if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
+            fail = __any_sync(0xffffffffu, fail);
+        };
+        auto group_or = [&](bool pred) -> bool {              // barrier over the 128 threads + OR
+            uint32_t r;
+            asm volatile(
+                "{\n.reg .pred pi, po;\n"
+                "setp.ne.b32 pi, %1, 0;\n"
+                "barrier.cta.red.or.pred po, 1, 128, pi;\n"
+                "selp.u32 %0, 1, 0, po;\n}\n"
+                : "=r"(r) : "r"(uint32_t(pred)) : "memory");
+            return r != 0;
+        };
+        bool stop = false;
+        for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
+            const SegInfo s = load_seg(m, seg);
+            if (s.n_tiles == 0) {
+                // nothing to attend: the state of an empty range
+                const uint32_t st = tid - 64;
+                for (uint32_t h = 0; h < HG; h++) {
+                    if (h0 + h >= H) break;
+                    float* rc = recs + (size_t(seg) * H + h0 + h) * kPart;
+                    for (uint32_t d = st; d < kRank; d += SOFTMAX_THREADS) rc[2 + d] = 0.0f;
+                    if (st == 0) { rc[0] = -INFINITY; rc[1] = 0.0f; }
+                }
+                continue;
+            }
+            m_used = -INFINITY;
+            l_run = 0.0f;
+            for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                const uint32_t sb = t & 1;
+                float* alpha_t = alpha_s + sb * HG;
+                wait_w(bar(B_SFULL0 + sb), (t >> 1) & 1);
+                uint32_t sv[2][32];
+                if (!fail) {
+                    tc_fence_after();
+                    tc_ld32(tmem + lane_base + COL_S + sb * TILE, sv[0]);
+                    tc_ld32(tmem + lane_base + COL_S + sb * TILE + 32, sv[1]);
+                    tc_wait_ld();
+                    tc_fence_before();
+                    mbar_arrive(bar(B_SEMPTY0 + sb));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[0][i] = sv[1][i] = 0u;
+                }
+                const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 64; i++) {
+                    float v = __uint_as_float(sv[i / 32][i % 32]) * scale_log2;
+                    v = (uint32_t(i) < valid) ? v : -INFINITY;
+                    sv[i / 32][i % 32] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+                float alpha = 1.0f;
+                bool need = false;
+                if (owner) {
+                    if (j == 0) {
+                        m_used = mx;
+                    } else if (mx > m_used + RESCALE_THRESHOLD) {
+                        alpha = exp2f(m_used - mx);
+                        m_used = mx;
+                        need = true;
+                    }
+                    alpha_t[hl] = alpha;
+                }
+                if (group_or(fail)) { stop = true; break; }
+                const bool any_need = group_or(need);
+                float sum = 0.0f;
+                uint32_t pk[32];
+                if (owner) {
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float p0 = exp2f(__uint_as_float(sv[i / 32][i % 32]) - m_used);
+                        const float p1 = exp2f(__uint_as_float(sv[(i + 1) / 32][(i + 1) % 32]) - m_used);
+                        sum += p0 + p1;
+                        pk[i / 2] = Elem<T>::pack2(p0, p1);
+                    }
+                    l_run = l_run * alpha + sum;
+                }
+                // PV of the previous tile must be complete: O is stable and P is free
+                wait_w(bar(B_PEMPTY), (t - 1) & 1);
+                if (fail) continue;            // carried to the next barrier
+                tc_fence_after();
+                if (any_need && j > 0) {
+                    // O^T[dim lane][head column] *= alpha[head]
+#pragma unroll 1
+                    for (int c = 0; c < 8; c++) {
+                        uint32_t o[32];
+                        const uint32_t col = COL_O + c * 32;
+                        tc_ld32(tmem + lane_base + col, o);
+                        tc_wait_ld();
+                        const int hbase = (c & 1) * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_t[hbase + i]);
+                        tc_st32(tmem + lane_base + col, o);
+                    }
+                    tc_wait_st();
+                }
+                if (owner) {
+                    // row hl of the K-major swizzled P tile: 8 chunks of 8 tokens
+                    unsigned char* prow = sm + OFF_P + hl * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) {
+                        uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                        *reinterpret_cast<uint4*>(prow + ((ch ^ (hl & 7)) * 16)) = v;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(bar(B_PFULL));
+            }
+            if (stop) break;
+            // ---- epilogue of the segment: O^T -> acc[head][dim], plus (m, l)
+            wait_w(bar(B_OFULL), nseg & 1);
+            if (group_or(fail)) { stop = true; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 8; c++) {
+                uint32_t o[32];
+                tc_ld32(tmem + lane_base + COL_O + c * 32, o);
+                tc_wait_ld();
+                const uint32_t dim = (c / 2) * 128 + q4 * 32 + lane;
+                const uint32_t hb = h0 + (c & 1) * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (hb + i < H) recs[(size_t(seg) * H + hb + i) * kPart + 2 + dim] = __uint_as_float(o[i]);
+                }
+            }
+            if (owner && h0 + hl < H) {
+                float* rc = recs + (size_t(seg) * H + h0 + hl) * kPart;
+                rc[0] = m_used;
+                rc[1] = l_run;
+            }
+            tc_fence_before();
+            nseg++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+int decode_tc5_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(decode_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(decode_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES);
+    return int(e);
+}
+
+int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t layer, uint32_t n_pages,
+                      const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
+{
+    (void)q_abs;
+    if (m.ctas == 0) return 0;
+    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);   // [0] = cache pool, [1] = Q'
+    const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
+    dim3 grid(m.ctas, (H + HG - 1) / HG);
+    if (dtype == 0)
+        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], layer, n_pages, m, recs, H,
+                                                                        scale_log2, status);
+    else
+        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], layer, n_pages, m,
+                                                                               recs, H, scale_log2, status);
+    return int(cudaGetLastError());
+}
+
+}  // namespace mla

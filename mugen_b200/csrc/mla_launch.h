@@ -22,9 +22,9 @@ int launch_decode_mma(int dtype, const void* q_abs, const void* layer_pool, uint
                       const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
 
 // Split-KV attention on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM,
-// cache tiles staged by TMA): grid (segments, ceil(H/64)).  tmap is the device-resident
-// CUtensorMap of the whole pool ([layers][slots][576]).
-int launch_decode_tc5(int dtype, const void* q_abs, const void* tmap, uint32_t layer,
+// cache tiles staged by TMA): grid (persistent blocks, ceil(H/64)).  tmaps points at two host
+// CUtensorMap objects: [0] the whole pool ([layers][slots][576]), [1] the absorbed queries.
+int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t layer,
                       uint32_t n_pages, const StepMeta& m, float* recs, uint32_t H, uint32_t* status,
                       cudaStream_t st);
 int decode_tc5_configure();   // sets the kernel's shared-memory attribute once
