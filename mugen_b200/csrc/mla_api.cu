@@ -26,7 +26,7 @@ thread_local std::string g_create_error;
 constexpr int kMetaRing = 4;
 
 struct LayerW {
-    void* w_uk = nullptr;
+    void* w_uk = nullptr;   // stored transposed per head: [h][512][128]
     void* w_uv = nullptr;
     void* norm = nullptr;
     bool set = false;
@@ -511,7 +511,14 @@ int mla_set_layer_weights(mla_ctx* c, uint32_t layer, const void* w_uk, const vo
     std::vector<uint16_t> buf;
     const size_t H = c->cfg.n_heads;
     if (int e = decode_weights(c, w_uk, w_type, H * mla::kNope, buf)) return e;
-    CU_TRY(c, cudaMemcpy(c->layers[layer].w_uk, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
+    {   // the absorb kernel reads W_UK transposed per head: [h][d][i] (contraction index contiguous)
+        std::vector<uint16_t> tr(buf.size());
+        for (size_t h = 0; h < H; h++)
+            for (size_t i = 0; i < size_t(mla::kNope); i++)
+                for (size_t d = 0; d < size_t(mla::kRank); d++)
+                    tr[(h * mla::kRank + d) * mla::kNope + i] = buf[(h * mla::kNope + i) * mla::kRank + d];
+        CU_TRY(c, cudaMemcpy(c->layers[layer].w_uk, tr.data(), tr.size() * 2, cudaMemcpyHostToDevice));
+    }
     if (int e = decode_weights(c, w_uv, w_type, H * mla::kVDim, buf)) return e;
     CU_TRY(c, cudaMemcpy(c->layers[layer].w_uv, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
     CU_TRY(c, cudaMemcpy(c->layers[layer].norm, kv_norm, mla::kRank * 2, cudaMemcpyHostToDevice));

@@ -7,7 +7,7 @@
 //   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims]
 //   QK       S[64 heads x 64 tok]   = Q'[64 x 576] . K^T          36 x tcgen05.mma  M=64  N=64 K=16
 //                                     A = Q' (K-major), B = cache sub-tiles (K-major)
-//   softmax  one thread per head reads its row of S from TMEM (tcgen05.ld), log2-domain online
+//   softmax  four threads per head read its row of S from TMEM (tcgen05.ld), log2-domain online
 //            softmax with lazy rescaling (the running reference maximum moves only when a tile
 //            exceeds it by more than 2^8), writes P (bf16/f16) to shared memory
 //   PV       O^T[512 dims x 64 heads] += V^T[512 x 64 tok] . P^T   16 x tcgen05.mma M=128 N=64 K=16
@@ -15,14 +15,19 @@
 //                                     no transpose), B = P (K-major)
 //
 // The transposed PV keeps all 128 TMEM lanes busy at M=128 and leaves O^T in 256 columns
-// (4 chunks of 128 latent dims x 64 head columns), S double-buffered in 2 x 64 more.
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 = softmax,
-// correction and epilogue (warp w touches TMEM lanes 32*(w%4) .. +31).
+// (4 chunks of 128 latent dims x 64 head columns); S is double-buffered, each buffer holding two
+// partial score tiles of 64 columns (one per QK issuer), which fills the 512 columns.
+// Warp roles: warp 0 = TMA producer, warps 1-4 = MMA issuers (two for QK, two for PV; warp 1 also
+// owns the TMEM allocation), warps 5-8 = softmax, correction and epilogue (warp w touches TMEM
+// lanes 32*(w%4) .. +31).
 // Output per (segment, head): m (reference maximum, log2 domain), l, acc[512] — 514 floats.
 //
 // Every mbarrier wait is bounded: after ~2 s a waiter raises ST_WAIT_TIMEOUT in the status word,
 // sets the block's abort flag and every role leaves its loops; TMEM is freed on all paths.
 #include <cuda.h>
+#ifdef MLA_TC5_TRACE
+#include <cstdio>
+#endif
 
 #include "mla_launch.h"
 
@@ -47,9 +52,9 @@ constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // +1024: manual 1 KB
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;                     // 4 x 64 columns
-constexpr uint32_t COL_S = 256;                   // 2 x 64 columns
+constexpr uint32_t COL_S = 256;                   // 2 buffers x 2 partial score tiles x 64 columns
 
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 288;                  // producer + 4 MMA issuers + 4 softmax warps
 constexpr int SOFTMAX_THREADS = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -115,18 +120,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 
 // ---- tcgen05 -------------------------------------------------------------------------------
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
+// The MMA-issuing thread is a single lane: every instruction it spends on building operands
+// delays the tensor core.  Descriptors are therefore kept as (low word, constant high word)
+// pairs; advancing an operand is one 32-bit add on the low word (address field, 16-byte units).
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -150,6 +165,24 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 16 lanes x 256 bits, repeated 8 times along the columns (64 columns): thread i receives, for
+// block k, registers 4k..4k+3 = (lane i/4, cols 8k+2(i%4), +1) and (lane i/4+8, same cols).
+__device__ __forceinline__ void tc_ld16x256_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
@@ -157,14 +190,13 @@ __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sy
 //   K-major : rows of 128 B (64 elements of K), 8-row groups 1024 B apart (SBO); LBO unused.
 //   MN-major: rows of 128 B (64 elements of M/N) indexed by K, 8-row groups SBO apart,
 //             64-element M/N blocks LBO apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= uint64_t((addr & 0x3FFFF) >> 4);
-    d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;     // SWIZZLE_128B
-    return d;
+// Low word: start address (bits 0-13, 16-byte units) and leading byte offset (bits 16-29).
+// High word: stride byte offset (bits 0-13), version 1 (bit 14), SWIZZLE_128B = 2 (bits 29-31).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
+    return (sbo_bytes >> 4) | (1u << 14) | (2u << 29);
 }
 // Instruction descriptor, kind::f16, f32 accumulate.
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
@@ -217,18 +249,18 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar(B_QFULL), 1);
-        mbar_init(bar(B_QEMPTY), 1);
+        mbar_init(bar(B_QEMPTY), 2);
         mbar_init(bar(B_KVFULL0), 1);
         mbar_init(bar(B_KVFULL1), 1);
-        mbar_init(bar(B_KVEMPTY0), 1);
-        mbar_init(bar(B_KVEMPTY1), 1);
-        mbar_init(bar(B_SFULL0), 1);
-        mbar_init(bar(B_SFULL1), 1);
+        mbar_init(bar(B_KVEMPTY0), 2);
+        mbar_init(bar(B_KVEMPTY1), 2);
+        mbar_init(bar(B_SFULL0), 2);
+        mbar_init(bar(B_SFULL1), 2);
         mbar_init(bar(B_SEMPTY0), SOFTMAX_THREADS);
         mbar_init(bar(B_SEMPTY1), SOFTMAX_THREADS);
         mbar_init(bar(B_PFULL), SOFTMAX_THREADS);
-        mbar_init(bar(B_PEMPTY), 1);
-        mbar_init(bar(B_OFULL), 1);
+        mbar_init(bar(B_PEMPTY), 2);
+        mbar_init(bar(B_OFULL), 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -240,13 +272,17 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
     if (warp == 0) {
         // ===================== TMA producer =====================
         if (lane == 0) {
             uint32_t t = 0, nseg = 0;
             bool ok = true;
+#ifdef MLA_TC5_TRACE
+            long long trace_prod_wait = 0;
+            const long long trace_t0 = clock64();
+#endif
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
@@ -259,7 +295,13 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
+#ifdef MLA_TC5_TRACE
+                    const long long tw0 = clock64();
+#endif
                     ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+#ifdef MLA_TC5_TRACE
+                    trace_prod_wait += clock64() - tw0;
+#endif
                     if (!ok) break;
                     uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
@@ -274,72 +316,103 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 }
                 nseg++;
             }
+#ifdef MLA_TC5_TRACE
+            if (blockIdx.x == 3 && blockIdx.y == 0)
+                printf("[producer] tiles %u total %lld wait_kv_empty %lld\n", t, clock64() - trace_t0, trace_prod_wait);
+#endif
         }
-    } else if (warp == 1) {
-        // ===================== MMA issuer =====================
-        if (lane == 0) {
-            constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 64, TILE, 0, 0);
-            constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 128, HG, 1, 0);
-            uint32_t t = 0, nseg = 0;
-            bool ok = true;
-            // PV of tile u (global tile counter): O^T += V^T . P^T
-            auto do_pv = [&](uint32_t u, bool first_of_seg) -> bool {
-                if (!mbar_wait(bar(B_PFULL), u & 1, abort_flag, status)) return false;
-                tc_fence_after();
-                const uint32_t kvb = sKV + (u % KV_STAGES) * KV_STAGE_BYTES;
-#pragma unroll
-                for (int c = 0; c < 4; c++) {           // 128 latent dims per chunk = 2 sub-tiles
-#pragma unroll
-                    for (int k = 0; k < TILE / 16; k++) {
-                        const uint64_t a = smem_desc(kvb + (2 * c) * SUB_BYTES + k * 2048, SUB_BYTES, 1024);
-                        const uint64_t b = smem_desc(sP + k * 32, 16, 1024);
-                        tc_mma(tmem + COL_O + c * HG, a, b, IDESC_PV, (first_of_seg && k == 0) ? 0u : 1u);
-                    }
-                }
-                tc_commit(bar(B_KVEMPTY0 + (u % KV_STAGES)));
-                tc_commit(bar(B_PEMPTY));
-                return true;
-            };
-            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
-                const SegInfo s = load_seg(m, seg);
-                if (s.n_tiles == 0) continue;
-                ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
-                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
-                    const uint32_t st = t % KV_STAGES, sb = t & 1;
+    } else if (warp <= 4) {
+        // ===================== MMA issuers =====================
+        // A tcgen05.mma costs its issuing warp about a hundred cycles before the next one can go,
+        // far more than the tensor core needs for these small shapes (N = 64, K = 16), so one
+        // issuer leaves the pipe mostly idle.  Four warps issue concurrently, each into its own
+        // accumulators: warps 1-2 split the 36 k-steps of QK into two partial score tiles
+        // (sub-tiles 0-4 and 5-8; the softmax adds them), warps 3-4 take two of the four
+        // 128-dim chunks of O^T each.  The warp runs the loop uniformly (operands stay in uniform
+        // registers) and one elected lane issues.
+        constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 64, TILE, 0, 0);
+        constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 128, HG, 1, 0);
+        constexpr uint32_t HI = desc_hi(1024);          // every operand: 8-row groups 1024 B apart
+        static_assert(KV_STAGES == 2, "descriptor bases below assume two cache stages");
+        const bool is_qk = warp <= 2;
+        const uint32_t part = (warp - 1) & 1;           // which half of the work
+        const uint32_t qk_a = desc_lo(sQ, 16);          // Q' (K-major)
+        const uint32_t kv_k0 = desc_lo(sKV, 16), kv_k1 = desc_lo(sKV + KV_STAGE_BYTES, 16);                 // tile as K
+        const uint32_t kv_v0 = desc_lo(sKV, SUB_BYTES), kv_v1 = desc_lo(sKV + KV_STAGE_BYTES, SUB_BYTES);   // tile as V^T
+        const uint32_t pv_b = desc_lo(sP, 16);          // P (K-major)
+        uint32_t t = 0, nseg = 0;
+        bool ok = true;
+        for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+            const SegInfo s = load_seg(m, seg);
+            if (s.n_tiles == 0) continue;
+            if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
+            for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                const uint32_t st = t % KV_STAGES, sb = t & 1;
+                if (is_qk) {
                     ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
                          mbar_wait(bar(B_SEMPTY0 + sb), ((t >> 1) & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t kvb = sKV + st * KV_STAGE_BYTES;
+                    const uint32_t b0 = st ? kv_k1 : kv_k0;
+                    const uint32_t d = tmem + COL_S + sb * (2 * TILE) + part * TILE;
+                    if (elect_one()) {
+                        if (part == 0) {
 #pragma unroll
-                    for (int c = 0; c < NSUB; c++) {
+                            for (int c = 0; c < 5; c++)
 #pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const uint64_t a = smem_desc(sQ + c * (HG * 128) + k * 32, 16, 1024);
-                            const uint64_t b = smem_desc(kvb + c * SUB_BYTES + k * 32, 16, 1024);
-                            tc_mma(tmem + COL_S + sb * TILE, a, b, IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
+                                for (int k = 0; k < 4; k++)
+                                    tc_mma(d, qk_a + ((c * (HG * 128) + k * 32) >> 4), HI, b0 + ((c * SUB_BYTES + k * 32) >> 4),
+                                           HI, IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
+                        } else {
+#pragma unroll
+                            for (int c = 5; c < NSUB; c++)
+#pragma unroll
+                                for (int k = 0; k < 4; k++)
+                                    tc_mma(d, qk_a + ((c * (HG * 128) + k * 32) >> 4), HI, b0 + ((c * SUB_BYTES + k * 32) >> 4),
+                                           HI, IDESC_QK, (c == 5 && k == 0) ? 0u : 1u);
                         }
+                        tc_commit(bar(B_SFULL0 + sb));
+                        if (j + 1 == s.n_tiles) tc_commit(bar(B_QEMPTY));
                     }
-                    tc_commit(bar(B_SFULL0 + sb));
-                    if (j + 1 == s.n_tiles) tc_commit(bar(B_QEMPTY));
-                    if (j > 0) ok = do_pv(t - 1, j == 1);
+                    __syncwarp();
+                } else {
+                    ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a0 = st ? kv_v1 : kv_v0;
+                    const uint32_t fresh = j == 0 ? 0u : 1u;
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < TILE / 16; k++)
+#pragma unroll
+                            for (int cc = 0; cc < 2; cc++) {      // 128 latent dims per chunk = 2 sub-tiles
+                                const uint32_t c = part * 2 + cc;
+                                tc_mma(tmem + COL_O + c * HG, a0 + ((2 * c * SUB_BYTES + k * 2048) >> 4), HI,
+                                       pv_b + ((k * 32) >> 4), HI, IDESC_PV, k == 0 ? fresh : 1u);
+                            }
+                        tc_commit(bar(B_KVEMPTY0 + st));
+                        tc_commit(bar(B_PEMPTY));
+                        if (j + 1 == s.n_tiles) tc_commit(bar(B_OFULL));
+                    }
+                    __syncwarp();
                 }
-                if (!ok) break;
-                ok = do_pv(t - 1, s.n_tiles == 1);
-                if (ok) tc_commit(bar(B_OFULL));
-                nseg++;
             }
+            nseg++;
         }
     } else {
         // ===================== softmax / correction / epilogue =====================
+        // S (M=64 layout) keeps the warp's 16 head rows in TMEM lanes 0-15 of its sub-partition.
+        // A 16x256b load spreads them over all 32 threads: thread i holds, for each block k of 8
+        // tokens, tokens 8k+2(i%4), +1 of head rows i/4 and i/4+8 — so a row is shared by the 4
+        // threads of a quad and row reductions are two shuffles.
         // The 128 threads meet at a named barrier every tile.  A failed (timed-out / aborted)
         // wait never makes a thread leave early on its own: the failure is carried to the next
         // barrier, OR-reduced there, and all 128 threads leave together.
         const uint32_t q4 = warp % 4;                         // TMEM sub-partition of this warp
         const uint32_t lane_base = (q4 * 32u) << 16;
-        const bool owner = lane < 16;                         // lanes 0-15 hold head rows of S (M=64 layout)
-        const uint32_t hl = q4 * 16 + lane;                   // head (within the group) owned by this thread
-        float m_used = -INFINITY, l_run = 0.0f;
+        const uint32_t qd = lane & 3;
+        const uint32_t r_a = q4 * 16 + lane / 4, r_b = r_a + 8;   // head rows (within the group)
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
         uint32_t t = 0, nseg = 0;
         bool fail = false;
         auto wait_w = [&](uint32_t b, uint32_t parity) {      // warp-uniform bounded wait
@@ -356,12 +429,24 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 : "=r"(r) : "r"(uint32_t(pred)) : "memory");
             return r != 0;
         };
+        auto quad_max = [](float v) {
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        };
+        auto quad_sum = [](float v) {
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            return v + __shfl_xor_sync(0xffffffffu, v, 2);
+        };
         bool stop = false;
+#ifdef MLA_TC5_TRACE
+        long long tr_wait_s = 0, tr_compute = 0, tr_wait_p = 0, tr_store = 0, tr_rescales = 0;
+        const long long tr_s0 = clock64();
+#endif
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
             const SegInfo s = load_seg(m, seg);
             if (s.n_tiles == 0) {
                 // nothing to attend: the state of an empty range
-                const uint32_t st = tid - 64;
+                const uint32_t st = tid - (NUM_THREADS - SOFTMAX_THREADS);
                 for (uint32_t h = 0; h < HG; h++) {
                     if (h0 + h >= H) break;
                     float* rc = recs + (size_t(seg) * H + h0 + h) * kPart;
@@ -370,61 +455,93 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 }
                 continue;
             }
-            m_used = -INFINITY;
-            l_run = 0.0f;
+            m_a = m_b = -INFINITY;
+            l_a = l_b = 0.0f;
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t sb = t & 1;
                 float* alpha_t = alpha_s + sb * HG;
+#ifdef MLA_TC5_TRACE
+                const long long ts0 = clock64();
+#endif
                 wait_w(bar(B_SFULL0 + sb), (t >> 1) & 1);
-                uint32_t sv[2][32];
+#ifdef MLA_TC5_TRACE
+                const long long ts1 = clock64();
+                tr_wait_s += ts1 - ts0;
+#endif
+                uint32_t sv[32];
                 if (!fail) {
                     tc_fence_after();
-                    tc_ld32(tmem + lane_base + COL_S + sb * TILE, sv[0]);
-                    tc_ld32(tmem + lane_base + COL_S + sb * TILE + 32, sv[1]);
+                    uint32_t sw[32];
+                    tc_ld16x256_x8(tmem + lane_base + COL_S + sb * (2 * TILE), sv);
+                    tc_ld16x256_x8(tmem + lane_base + COL_S + sb * (2 * TILE) + TILE, sw);
                     tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
                     tc_fence_before();
                     mbar_arrive(bar(B_SEMPTY0 + sb));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) sv[0][i] = sv[1][i] = 0u;
+                    for (int i = 0; i < 32; i++) sv[i] = 0u;
                 }
                 const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
-                float mx = -INFINITY;
+                float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; i++) {
-                    float v = __uint_as_float(sv[i / 32][i % 32]) * scale_log2;
-                    v = (uint32_t(i) < valid) ? v : -INFINITY;
-                    sv[i / 32][i % 32] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                for (int k = 0; k < 8; k++) {
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const bool in = uint32_t(8 * k + 2 * qd + e) < valid;
+                        const float va = in ? __uint_as_float(sv[4 * k + e]) * scale_log2 : -INFINITY;
+                        const float vb = in ? __uint_as_float(sv[4 * k + 2 + e]) * scale_log2 : -INFINITY;
+                        sv[4 * k + e] = __float_as_uint(va);
+                        sv[4 * k + 2 + e] = __float_as_uint(vb);
+                        mx_a = fmaxf(mx_a, va);
+                        mx_b = fmaxf(mx_b, vb);
+                    }
                 }
-                float alpha = 1.0f;
+                mx_a = quad_max(mx_a);
+                mx_b = quad_max(mx_b);
+                float alpha_a = 1.0f, alpha_b = 1.0f;
                 bool need = false;
-                if (owner) {
-                    if (j == 0) {
-                        m_used = mx;
-                    } else if (mx > m_used + RESCALE_THRESHOLD) {
-                        alpha = exp2f(m_used - mx);
-                        m_used = mx;
-                        need = true;
-                    }
-                    alpha_t[hl] = alpha;
+                if (j == 0) {
+                    m_a = mx_a;
+                    m_b = mx_b;
+                } else {
+                    if (mx_a > m_a + RESCALE_THRESHOLD) { alpha_a = fast_ex2(m_a - mx_a); m_a = mx_a; need = true; }
+                    if (mx_b > m_b + RESCALE_THRESHOLD) { alpha_b = fast_ex2(m_b - mx_b); m_b = mx_b; need = true; }
                 }
-                if (group_or(fail)) { stop = true; break; }
-                const bool any_need = group_or(need);
-                float sum = 0.0f;
-                uint32_t pk[32];
-                if (owner) {
+                if (qd == 0) {
+                    alpha_t[r_a] = alpha_a;
+                    alpha_t[r_b] = alpha_b;
+                }
+                // one barrier on the common path; a second one only to tell failure from rescale
+                bool any_need = group_or(need || fail);
+                if (any_need && group_or(fail)) { stop = true; break; }
+                float sum_a = 0.0f, sum_b = 0.0f;
+                uint32_t pk_a[8], pk_b[8];
 #pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float p0 = exp2f(__uint_as_float(sv[i / 32][i % 32]) - m_used);
-                        const float p1 = exp2f(__uint_as_float(sv[(i + 1) / 32][(i + 1) % 32]) - m_used);
-                        sum += p0 + p1;
-                        pk[i / 2] = Elem<T>::pack2(p0, p1);
-                    }
-                    l_run = l_run * alpha + sum;
+                for (int k = 0; k < 8; k++) {
+                    const float a0 = fast_ex2(__uint_as_float(sv[4 * k]) - m_a);
+                    const float a1 = fast_ex2(__uint_as_float(sv[4 * k + 1]) - m_a);
+                    const float b0 = fast_ex2(__uint_as_float(sv[4 * k + 2]) - m_b);
+                    const float b1 = fast_ex2(__uint_as_float(sv[4 * k + 3]) - m_b);
+                    sum_a += a0 + a1;
+                    sum_b += b0 + b1;
+                    pk_a[k] = Elem<T>::pack2(a0, a1);
+                    pk_b[k] = Elem<T>::pack2(b0, b1);
                 }
+                l_a = l_a * alpha_a + quad_sum(sum_a);
+                l_b = l_b * alpha_b + quad_sum(sum_b);
                 // PV of the previous tile must be complete: O is stable and P is free
+#ifdef MLA_TC5_TRACE
+                const long long ts2 = clock64();
+                tr_compute += ts2 - ts1;
+#endif
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
+#ifdef MLA_TC5_TRACE
+                const long long ts3 = clock64();
+                tr_wait_p += ts3 - ts2;
+                if (any_need && j > 0) tr_rescales++;
+#endif
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
                 if (any_need && j > 0) {
@@ -443,18 +560,22 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                     }
                     tc_wait_st();
                 }
-                if (owner) {
-                    // row hl of the K-major swizzled P tile: 8 chunks of 8 tokens
-                    unsigned char* prow = sm + OFF_P + hl * 128;
+                {
+                    // rows r_a, r_b of the K-major swizzled P tile; chunk k = tokens 8k..8k+7
+                    unsigned char* pa = sm + OFF_P + r_a * 128 + qd * 4;
+                    unsigned char* pb = sm + OFF_P + r_b * 128 + qd * 4;
 #pragma unroll
-                    for (int ch = 0; ch < 8; ch++) {
-                        uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-                        *reinterpret_cast<uint4*>(prow + ((ch ^ (hl & 7)) * 16)) = v;
+                    for (int k = 0; k < 8; k++) {
+                        *reinterpret_cast<uint32_t*>(pa + ((k ^ (r_a & 7)) << 4)) = pk_a[k];
+                        *reinterpret_cast<uint32_t*>(pb + ((k ^ (r_b & 7)) << 4)) = pk_b[k];
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(bar(B_PFULL));
+#ifdef MLA_TC5_TRACE
+                tr_store += clock64() - ts3;
+#endif
             }
             if (stop) break;
             // ---- epilogue of the segment: O^T -> acc[head][dim], plus (m, l)
@@ -473,14 +594,26 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                     if (hb + i < H) recs[(size_t(seg) * H + hb + i) * kPart + 2 + dim] = __uint_as_float(o[i]);
                 }
             }
-            if (owner && h0 + hl < H) {
-                float* rc = recs + (size_t(seg) * H + h0 + hl) * kPart;
-                rc[0] = m_used;
-                rc[1] = l_run;
+            if (qd == 0) {
+                if (h0 + r_a < H) {
+                    float* rc = recs + (size_t(seg) * H + h0 + r_a) * kPart;
+                    rc[0] = m_a;
+                    rc[1] = l_a;
+                }
+                if (h0 + r_b < H) {
+                    float* rc = recs + (size_t(seg) * H + h0 + r_b) * kPart;
+                    rc[0] = m_b;
+                    rc[1] = l_b;
+                }
             }
             tc_fence_before();
             nseg++;
         }
+#ifdef MLA_TC5_TRACE
+        if (blockIdx.x == 3 && blockIdx.y == 0 && tid == 160)
+            printf("[softmax] tiles %u total %lld wait_s_full %lld compute %lld wait_p_empty %lld rescale+store %lld rescales %lld\n",
+                   t, clock64() - tr_s0, tr_wait_s, tr_compute, tr_wait_p, tr_store, tr_rescales);
+#endif
     }
 
     tc_fence_before();

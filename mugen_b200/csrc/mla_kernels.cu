@@ -118,63 +118,85 @@ void launch_write_rows(const void* src, void* layer_pool, uint64_t pool_slots, c
 //   q_abs[r][h][d] = sum_{i<128} q[r][h][i] * W_UK[h*128+i][d],   d < 512
 // and q_rope copied behind it, so that a query row has the layout of a cache row
 // (512 latent dims, then 64 rope dims) and the score is one 576-long dot product.
-// Grid (head, row tile); W_UK_h is streamed once per block and reused for RT rows.
 // ------------------------------------------------------------------------------------------
-template <typename T, int RT>
-__global__ void __launch_bounds__(256)
-absorb_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, T* __restrict__ q_abs,
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Block = (head, 16 query rows); C[16 x 512] = q_nope[16 x 128] . W_UK_h[128 x 512] on the
+// warp-level tensor path (m16n8k16, f32 accumulate).  The weight is read from its transposed copy
+// W_UK^T[h][d][i] (made once at registration) so that B fragments are plain 4-byte loads with the
+// contraction index contiguous.  Warp w owns output columns [128w, 128w+128).
+template <typename T>
+__global__ void __launch_bounds__(128)
+absorb_kernel(const T* __restrict__ q, const T* __restrict__ w_uk_t, T* __restrict__ q_abs,
               uint32_t rows, uint32_t H)
 {
-    __shared__ float qs[RT][kNope];
-    const uint32_t h = blockIdx.x, r0 = blockIdx.y * RT, tid = threadIdx.x;
-    for (int idx = tid; idx < RT * kNope; idx += 256) {
-        const uint32_t rr = idx / kNope, i = idx % kNope, r = r0 + rr;
-        qs[rr][i] = r < rows ? Elem<T>::to_f32(q[(size_t(r) * H + h) * kQDim + i]) : 0.0f;
-    }
-    for (int idx = tid; idx < RT * kRope; idx += 256) {
-        const uint32_t rr = idx / kRope, k = idx % kRope, r = r0 + rr;
+    const uint32_t h = blockIdx.x, r0 = blockIdx.y * 16, tid = threadIdx.x;
+    const uint32_t warp = tid / 32, lane = tid % 32, g = lane / 4, t4 = lane % 4;
+    for (int idx = tid; idx < 16 * (kRope / 2); idx += 128) {        // rope part: straight copy
+        const uint32_t rr = idx / (kRope / 2), k = idx % (kRope / 2), r = r0 + rr;
         if (r < rows)
-            q_abs[(size_t(r) * H + h) * kRow + kRank + k] = q[(size_t(r) * H + h) * kQDim + kNope + k];
+            reinterpret_cast<uint32_t*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[k] =
+                reinterpret_cast<const uint32_t*>(q + (size_t(r) * H + h) * kQDim + kNope)[k];
     }
-    __syncthreads();
-    const int d0 = tid * 2;
-    float acc[RT][2];
+    uint32_t a[kNope / 16][4];
+    {
+        const bool v0 = r0 + g < rows, v1 = r0 + g + 8 < rows;
+        const T* q0 = q + (size_t(r0 + g) * H + h) * kQDim;
+        const T* q1 = q + (size_t(r0 + g + 8) * H + h) * kQDim;
 #pragma unroll
-    for (int rr = 0; rr < RT; rr++) acc[rr][0] = acc[rr][1] = 0.0f;
-    const T* wp = w_uk + size_t(h) * kNope * kRank + d0;
-#pragma unroll 4
-    for (int i = 0; i < kNope; i++) {
-        const typename Elem<T>::pair w2 = *reinterpret_cast<const typename Elem<T>::pair*>(wp + size_t(i) * kRank);
-        const float w0 = Elem<T>::to_f32(w2.x), w1 = Elem<T>::to_f32(w2.y);
-#pragma unroll
-        for (int rr = 0; rr < RT; rr++) {
-            const float qv = qs[rr][i];
-            acc[rr][0] = fmaf(qv, w0, acc[rr][0]);
-            acc[rr][1] = fmaf(qv, w1, acc[rr][1]);
+        for (int ks = 0; ks < kNope / 16; ks++) {
+            const int col = ks * 16 + t4 * 2;
+            a[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+            a[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+            a[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+            a[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
         }
     }
+    const T* wt = w_uk_t + (size_t(h) * kRank + warp * 128) * kNope;
+#pragma unroll 2
+    for (int nt = 0; nt < 16; nt++) {
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const T* wrow = wt + size_t(nt * 8 + g) * kNope + t4 * 2;
+        uint32_t b[kNope / 16][2];
 #pragma unroll
-    for (int rr = 0; rr < RT; rr++) {
-        const uint32_t r = r0 + rr;
-        if (r < rows)
-            *reinterpret_cast<uint32_t*>(q_abs + (size_t(r) * H + h) * kRow + d0) =
-                Elem<T>::pack2(acc[rr][0], acc[rr][1]);
+        for (int ks = 0; ks < kNope / 16; ks++) {
+            b[ks][0] = *reinterpret_cast<const uint32_t*>(wrow + ks * 16);
+            b[ks][1] = *reinterpret_cast<const uint32_t*>(wrow + ks * 16 + 8);
+        }
+#pragma unroll
+        for (int ks = 0; ks < kNope / 16; ks++) mma16816<T>(c, a[ks], b[ks][0], b[ks][1]);
+        const int col = warp * 128 + nt * 8 + t4 * 2;
+        if (r0 + g < rows)
+            *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g) * H + h) * kRow + col) = Elem<T>::pack2(c[0], c[1]);
+        if (r0 + g + 8 < rows)
+            *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g + 8) * H + h) * kRow + col) = Elem<T>::pack2(c[2], c[3]);
     }
 }
 
-void launch_absorb(int dtype, const void* q, const void* w_uk, void* q_abs, uint32_t rows,
+void launch_absorb(int dtype, const void* q, const void* w_uk_t, void* q_abs, uint32_t rows,
                    uint32_t H, cudaStream_t st)
 {
     if (rows == 0) return;
-    constexpr int RT = 8;
-    dim3 grid(H, (rows + RT - 1) / RT);
+    dim3 grid(H, (rows + 15) / 16);
     if (dtype == 0)
-        absorb_kernel<__half, RT><<<grid, 256, 0, st>>>(static_cast<const __half*>(q),
-                                                        static_cast<const __half*>(w_uk),
-                                                        static_cast<__half*>(q_abs), rows, H);
+        absorb_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(q), static_cast<const __half*>(w_uk_t),
+                                                    static_cast<__half*>(q_abs), rows, H);
     else
-        absorb_kernel<__nv_bfloat16, RT><<<grid, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(w_uk),
+        absorb_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(w_uk_t),
             static_cast<__nv_bfloat16*>(q_abs), rows, H);
 }
 
@@ -267,11 +289,132 @@ merge_outproj_kernel(const float* __restrict__ recs, const uint32_t* __restrict_
     }
 }
 
+// Same merge, projection on the warp-level tensor path.  Block = (head, 16 query rows):
+//   1. threads 0-15 find each row's M and 1/L over its parts;
+//   2. the merged, normalised o_c[16 x 512] is built in shared memory as TWO 16-bit matrices,
+//      hi = T(o) and lo = T(o - hi): together they carry ~16 (bf16) / 22 (fp16) mantissa bits, so
+//      the float state is not rounded to the storage type before W_UV;
+//   3. out[16 x 128] = (hi + lo)[16 x 512] . W_UV_h^T, m16n8k16 with f32 accumulate; warp w owns
+//      outputs [32w, 32w+32); W_UV rows are K-contiguous, so B fragments are plain 4-byte loads.
+template <typename T>
+__global__ void __launch_bounds__(128)
+merge_outproj_mma_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin,
+                         uint32_t n_parts, const T* __restrict__ w_uv, T* __restrict__ out, uint32_t rows,
+                         uint32_t H)
+{
+    constexpr int PITCH = kRank + 8;                 // elements; keeps ldmatrix rows on distinct banks
+    __shared__ __align__(16) T a_hi[16 * PITCH];
+    __shared__ __align__(16) T a_lo[16 * PITCH];
+    __shared__ float row_m[16], row_inv[16];
+    __shared__ uint32_t row_pb[16], row_pe[16];
+    const uint32_t h = blockIdx.x, r0 = blockIdx.y * 16, tid = threadIdx.x;
+    const uint32_t warp = tid / 32, lane = tid % 32, g = lane / 4, t4 = lane % 4;
+    auto rec_of = [&](uint32_t r, uint32_t p) -> const float* {
+        const size_t idx = row_seg_begin ? (size_t(p) * H + h) : ((size_t(p) * rows + r) * H + h);
+        return recs + idx * kPart;
+    };
+    if (tid < 16) {
+        const uint32_t r = r0 + tid;
+        uint32_t pb = 0, pe = 0;
+        float M = -INFINITY, L = 0.0f;
+        if (r < rows) {
+            if (row_seg_begin) { pb = row_seg_begin[r]; pe = row_seg_begin[r + 1]; }
+            else               { pb = 0; pe = n_parts; }
+            for (uint32_t p = pb; p < pe; p++) M = fmaxf(M, rec_of(r, p)[0]);
+            if (M > -INFINITY)
+                for (uint32_t p = pb; p < pe; p++) {
+                    const float* rc = rec_of(r, p);
+                    L = fmaf(exp2f(rc[0] - M), rc[1], L);
+                }
+        }
+        row_m[tid] = M;
+        row_inv[tid] = L > 0.0f ? 1.0f / L : 0.0f;
+        row_pb[tid] = pb;
+        row_pe[tid] = pe;
+    }
+    __syncthreads();
+    {   // thread -> row tid/8, dims (tid%8)*64 .. +63, sixteen at a time
+        const uint32_t rr = tid / 8, r = r0 + rr, d_base = (tid % 8) * 64;
+        const float M = row_m[rr], inv = row_inv[rr];
+        const uint32_t pb = row_pb[rr], pe = row_pe[rr];
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ch++) {
+            const uint32_t d0 = d_base + ch * 16;
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+            if (inv > 0.0f)
+                for (uint32_t p = pb; p < pe; p++) {
+                    const float* rc = rec_of(r, p);
+                    const float w = exp2f(rc[0] - M);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float2 v = *reinterpret_cast<const float2*>(rc + 2 + d0 + 2 * i);
+                        acc[2 * i] = fmaf(w, v.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w, v.y, acc[2 * i + 1]);
+                    }
+                }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float o0 = acc[2 * i] * inv, o1 = acc[2 * i + 1] * inv;
+                const T h0 = Elem<T>::from_f32(o0), h1 = Elem<T>::from_f32(o1);
+                const uint32_t hp = Elem<T>::pack2(o0, o1);
+                const uint32_t lp = Elem<T>::pack2(o0 - Elem<T>::to_f32(h0), o1 - Elem<T>::to_f32(h1));
+                *reinterpret_cast<uint32_t*>(a_hi + rr * PITCH + d0 + 2 * i) = hp;
+                *reinterpret_cast<uint32_t*>(a_lo + rr * PITCH + d0 + 2 * i) = lp;
+            }
+        }
+    }
+    __syncthreads();
+    float c[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.0f;
+    const T* wb = w_uv + (size_t(h) * kVDim + warp * 32 + g) * kRank + t4 * 2;
+    const int mi = lane / 8, lr = lane % 8;
+    const uint32_t hi_addr = static_cast<uint32_t>(__cvta_generic_to_shared(a_hi + ((mi % 2) * 8 + lr) * PITCH + (mi / 2) * 8));
+    const uint32_t lo_addr = static_cast<uint32_t>(__cvta_generic_to_shared(a_lo + ((mi % 2) * 8 + lr) * PITCH + (mi / 2) * 8));
+#pragma unroll 4
+    for (int ks = 0; ks < kRank / 16; ks++) {
+        uint32_t ah[4], al[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(ah[0]), "=r"(ah[1]), "=r"(ah[2]), "=r"(ah[3]) : "r"(hi_addr + ks * 32));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(al[0]), "=r"(al[1]), "=r"(al[2]), "=r"(al[3]) : "r"(lo_addr + ks * 32));
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const T* wp = wb + size_t(nt * 8) * kRank + ks * 16;
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(wp);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(wp + 8);
+            mma16816<T>(c[nt], ah, b0, b1);
+            mma16816<T>(c[nt], al, b0, b1);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+        const int col = warp * 32 + nt * 8 + t4 * 2;
+        if (r0 + g < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g) * H + h) * kVDim + col) = Elem<T>::pack2(c[nt][0], c[nt][1]);
+        if (r0 + g + 8 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g + 8) * H + h) * kVDim + col) = Elem<T>::pack2(c[nt][2], c[nt][3]);
+    }
+}
+
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
                   cudaStream_t st)
 {
     if (rows == 0) return;
+    if (!exported) {
+        dim3 grid16(H, (rows + 15) / 16);
+        if (dtype == 0)
+            merge_outproj_mma_kernel<__half><<<grid16, 128, 0, st>>>(
+                recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv), static_cast<__half*>(out), rows, H);
+        else
+            merge_outproj_mma_kernel<__nv_bfloat16><<<grid16, 128, 0, st>>>(
+                recs, row_seg_begin, n_parts, static_cast<const __nv_bfloat16*>(w_uv),
+                static_cast<__nv_bfloat16*>(out), rows, H);
+        return;
+    }
     constexpr int RT = 8;
     dim3 grid(H, (rows + RT - 1) / RT);
     if (dtype == 0)

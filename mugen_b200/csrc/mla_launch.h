@@ -13,7 +13,8 @@ void launch_append(int dtype, const void* kv_a, void* layer_pool, uint64_t pool_
 void launch_write_rows(const void* src, void* layer_pool, uint64_t pool_slots, const uint32_t* table,
                        uint32_t row_begin, uint32_t n, uint32_t* status, cudaStream_t st);
 
-void launch_absorb(int dtype, const void* q, const void* w_uk, void* q_abs, uint32_t rows,
+// w_uk_t: W_UK transposed per head, [H][512][128].
+void launch_absorb(int dtype, const void* q, const void* w_uk_t, void* q_abs, uint32_t rows,
                    uint32_t H, cudaStream_t st);
 
 // Split-KV attention, legacy tensor path (mma.sync m16n8k16): grid (segments, ceil(H/16)).
