@@ -15,10 +15,11 @@
 //                                     no transpose), B = P (K-major)
 //
 // The transposed PV keeps all 128 TMEM lanes busy at M=128 and leaves O^T in 256 columns
-// (4 chunks of 128 latent dims x 64 head columns); S is double-buffered, each buffer holding two
-// partial score tiles of 64 columns (one per QK issuer), which fills the 512 columns.
-// Warp roles: warp 0 = TMA producer, warps 1-4 = MMA issuers (two for QK, two for PV; warp 1 also
-// owns the TMEM allocation), warps 5-8 = softmax, correction and epilogue (warp w touches TMEM
+// (4 chunks of 128 latent dims x 64 head columns); the other 256 hold four partial score tiles of
+// 64 columns, one per QK issuer (the softmax copies them to registers at once and hands the
+// columns back, so the next tile's QK overlaps the exponentials).
+// Warp roles: warp 0 = TMA producer, warps 1-6 = MMA issuers (four for QK, two for PV; warp 1 also
+// owns the TMEM allocation), warps 7-10 = softmax, correction and epilogue (warp w touches TMEM
 // lanes 32*(w%4) .. +31).
 // Output per (segment, head): m (reference maximum, log2 domain), l, acc[512] — 514 floats.
 //
@@ -52,9 +53,10 @@ constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // +1024: manual 1 KB
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;                     // 4 x 64 columns
-constexpr uint32_t COL_S = 256;                   // 2 buffers x 2 partial score tiles x 64 columns
+constexpr uint32_t COL_S = 256;                   // 4 partial score tiles x 64 columns
 
-constexpr int NUM_THREADS = 288;                  // producer + 4 MMA issuers + 4 softmax warps
+constexpr int N_QK = 4, N_PV = 2;                 // MMA-issuing warps for QK and for PV
+constexpr int NUM_THREADS = 32 * (1 + N_QK + N_PV + 4);   // producer + issuers + 4 softmax warps
 constexpr int SOFTMAX_THREADS = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -249,18 +251,18 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar(B_QFULL), 1);
-        mbar_init(bar(B_QEMPTY), 2);
+        mbar_init(bar(B_QEMPTY), N_QK);
         mbar_init(bar(B_KVFULL0), 1);
         mbar_init(bar(B_KVFULL1), 1);
-        mbar_init(bar(B_KVEMPTY0), 2);
-        mbar_init(bar(B_KVEMPTY1), 2);
-        mbar_init(bar(B_SFULL0), 2);
-        mbar_init(bar(B_SFULL1), 2);
+        mbar_init(bar(B_KVEMPTY0), N_PV);
+        mbar_init(bar(B_KVEMPTY1), N_PV);
+        mbar_init(bar(B_SFULL0), N_QK);
+        mbar_init(bar(B_SFULL1), N_QK);
         mbar_init(bar(B_SEMPTY0), SOFTMAX_THREADS);
         mbar_init(bar(B_SEMPTY1), SOFTMAX_THREADS);
         mbar_init(bar(B_PFULL), SOFTMAX_THREADS);
-        mbar_init(bar(B_PEMPTY), 2);
-        mbar_init(bar(B_OFULL), 2);
+        mbar_init(bar(B_PEMPTY), N_PV);
+        mbar_init(bar(B_OFULL), N_PV);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -321,21 +323,22 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 printf("[producer] tiles %u total %lld wait_kv_empty %lld\n", t, clock64() - trace_t0, trace_prod_wait);
 #endif
         }
-    } else if (warp <= 4) {
+    } else if (warp <= N_QK + N_PV) {
         // ===================== MMA issuers =====================
         // A tcgen05.mma costs its issuing warp about a hundred cycles before the next one can go,
         // far more than the tensor core needs for these small shapes (N = 64, K = 16), so one
-        // issuer leaves the pipe mostly idle.  Four warps issue concurrently, each into its own
-        // accumulators: warps 1-2 split the 36 k-steps of QK into two partial score tiles
-        // (sub-tiles 0-4 and 5-8; the softmax adds them), warps 3-4 take two of the four
+        // issuer leaves the pipe mostly idle.  Six warps issue concurrently, each into its own
+        // accumulators: warps 1-4 split the 36 k-steps of QK into four partial score tiles
+        // (sub-tiles 0-2, 3-4, 5-6, 7-8; the softmax adds them), warps 5-6 take two of the four
         // 128-dim chunks of O^T each.  The warp runs the loop uniformly (operands stay in uniform
         // registers) and one elected lane issues.
         constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 64, TILE, 0, 0);
         constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 128, HG, 1, 0);
         constexpr uint32_t HI = desc_hi(1024);          // every operand: 8-row groups 1024 B apart
         static_assert(KV_STAGES == 2, "descriptor bases below assume two cache stages");
-        const bool is_qk = warp <= 2;
-        const uint32_t part = (warp - 1) & 1;           // which half of the work
+        const bool is_qk = warp <= N_QK;
+        const uint32_t part = is_qk ? warp - 1 : warp - 1 - N_QK;
+        const int c_lo = part == 0 ? 0 : 1 + 2 * int(part), c_hi = 3 + 2 * int(part);   // QK sub-tile range
         const uint32_t qk_a = desc_lo(sQ, 16);          // Q' (K-major)
         const uint32_t kv_k0 = desc_lo(sKV, 16), kv_k1 = desc_lo(sKV + KV_STAGE_BYTES, 16);                 // tile as K
         const uint32_t kv_v0 = desc_lo(sKV, SUB_BYTES), kv_v1 = desc_lo(sKV + KV_STAGE_BYTES, SUB_BYTES);   // tile as V^T
@@ -347,31 +350,25 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
             if (s.n_tiles == 0) continue;
             if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
             for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
-                const uint32_t st = t % KV_STAGES, sb = t & 1;
+                const uint32_t st = t % KV_STAGES;
                 if (is_qk) {
                     ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
-                         mbar_wait(bar(B_SEMPTY0 + sb), ((t >> 1) & 1) ^ 1, abort_flag, status);
+                         mbar_wait(bar(B_SEMPTY0), (t & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t b0 = st ? kv_k1 : kv_k0;
-                    const uint32_t d = tmem + COL_S + sb * (2 * TILE) + part * TILE;
+                    const uint32_t d = tmem + COL_S + part * TILE;
                     if (elect_one()) {
-                        if (part == 0) {
 #pragma unroll
-                            for (int c = 0; c < 5; c++)
-#pragma unroll
-                                for (int k = 0; k < 4; k++)
-                                    tc_mma(d, qk_a + ((c * (HG * 128) + k * 32) >> 4), HI, b0 + ((c * SUB_BYTES + k * 32) >> 4),
-                                           HI, IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
-                        } else {
-#pragma unroll
-                            for (int c = 5; c < NSUB; c++)
+                        for (int c = 0; c < NSUB; c++) {
+                            if (c >= c_lo && c < c_hi) {
 #pragma unroll
                                 for (int k = 0; k < 4; k++)
                                     tc_mma(d, qk_a + ((c * (HG * 128) + k * 32) >> 4), HI, b0 + ((c * SUB_BYTES + k * 32) >> 4),
-                                           HI, IDESC_QK, (c == 5 && k == 0) ? 0u : 1u);
+                                           HI, IDESC_QK, (c == c_lo && k == 0) ? 0u : 1u);
+                            }
                         }
-                        tc_commit(bar(B_SFULL0 + sb));
+                        tc_commit(bar(B_SFULL0));
                         if (j + 1 == s.n_tiles) tc_commit(bar(B_QEMPTY));
                     }
                     __syncwarp();
@@ -463,7 +460,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
 #ifdef MLA_TC5_TRACE
                 const long long ts0 = clock64();
 #endif
-                wait_w(bar(B_SFULL0 + sb), (t >> 1) & 1);
+                wait_w(bar(B_SFULL0), t & 1);
 #ifdef MLA_TC5_TRACE
                 const long long ts1 = clock64();
                 tr_wait_s += ts1 - ts0;
@@ -472,13 +469,21 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 if (!fail) {
                     tc_fence_after();
                     uint32_t sw[32];
-                    tc_ld16x256_x8(tmem + lane_base + COL_S + sb * (2 * TILE), sv);
-                    tc_ld16x256_x8(tmem + lane_base + COL_S + sb * (2 * TILE) + TILE, sw);
+                    tc_ld16x256_x8(tmem + lane_base + COL_S, sv);
+                    tc_ld16x256_x8(tmem + lane_base + COL_S + TILE, sw);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    tc_ld16x256_x8(tmem + lane_base + COL_S + 2 * TILE, sw);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    tc_ld16x256_x8(tmem + lane_base + COL_S + 3 * TILE, sw);
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
                     tc_fence_before();
-                    mbar_arrive(bar(B_SEMPTY0 + sb));
+                    mbar_arrive(bar(B_SEMPTY0));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i++) sv[i] = 0u;
@@ -610,7 +615,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
             nseg++;
         }
 #ifdef MLA_TC5_TRACE
-        if (blockIdx.x == 3 && blockIdx.y == 0 && tid == 160)
+        if (blockIdx.x == 3 && blockIdx.y == 0 && tid == NUM_THREADS - SOFTMAX_THREADS)
             printf("[softmax] tiles %u total %lld wait_s_full %lld compute %lld wait_p_empty %lld rescale+store %lld rescales %lld\n",
                    t, clock64() - tr_s0, tr_wait_s, tr_compute, tr_wait_p, tr_store, tr_rescales);
 #endif
