@@ -42,6 +42,7 @@ constexpr int NSUB = kRow / 64;                   // 9 sub-tiles of 64 dims
 constexpr int SUB_BYTES = TILE * 128;             // 8 KB
 constexpr int KV_STAGE_BYTES = NSUB * SUB_BYTES;  // 73,728
 constexpr int KV_STAGES = 2;
+constexpr int PREFETCH_TILES = 4;                 // L2 prefetch distance of the producer, in tiles
 constexpr int Q_BYTES = NSUB * HG * 128;          // 73,728
 constexpr int P_BYTES = HG * 128;                 // 8,192
 constexpr int OFF_Q = 0;
@@ -114,6 +115,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Pulls a box into L2 only: issued a few tiles ahead so that, when a shared-memory stage frees
+// up, the real load is an L2 hit and the stage turns around in hundreds of cycles, not thousands.
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile(
@@ -295,8 +302,15 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 for (int j = 0; j < NSUB; j++)
                     tma_load_2d(sQ + j * (HG * 128), &map_q, bar(B_QFULL), j * 64, int(s.row * H + h0));
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
+                auto prefetch_tile = [&](uint32_t jj) {
+                    const uint32_t pg = tbl[s.page_begin + jj];
+                    if (pg < n_pages)
+                        for (int c = 0; c < NSUB; c++) tma_prefetch_3d(&map_kv, c * 64, int(pg * kPage), int(layer));
+                };
+                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
+                    if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
 #ifdef MLA_TC5_TRACE
                     const long long tw0 = clock64();
 #endif
