@@ -301,6 +301,7 @@ def run_ours(a):
             for l in range(L):
                 ctx.step_layer_host(l, hkv[l], hq[l], hout[l])
             ctx.step_end()
+            torch.cuda.current_stream().synchronize()   # the step's result is read on the host
 
         for _ in range(a.warmup):
             host_step()
@@ -318,7 +319,7 @@ def run_ours(a):
         e2e = {"value": tokens / (float(et[0]) * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(world * L * (B * 576 * 2 + B * H * 192 * 2)),
                "d2h_bytes_per_step": int(world * L * B * H * 128 * 2),
-               "api": "mla_step_begin / mla_step_layer_host (host buffers) / mla_step_end"}
+               "api": "mla_step_begin / mla_step_layer_host (page-locked host buffers) / mla_step_end, stream synchronised every step"}
         assert ctx.status() == 0
 
     cpu = None

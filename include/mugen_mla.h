@@ -156,7 +156,10 @@ int mla_step_append(mla_ctx* ctx, uint32_t layer, const void* kv_a, void* stream
 /* q: DEVICE [rows][n_heads][192]; out: DEVICE [rows][n_heads][128]. */
 int mla_step_attend(mla_ctx* ctx, uint32_t layer, const void* q, void* out, void* stream);
 /* Same two calls with HOST buffers: copies kv_a and q in, runs append + attend, copies out
- * back, all on `stream` (pinned staging inside the context). */
+ * back, all on `stream`.  Page-locked caller buffers are copied directly and the call returns
+ * without waiting (synchronise the stream, or call mla_status, before reading out_host);
+ * pageable buffers are staged through page-locked memory inside the context and the call
+ * returns when out_host is filled. */
 int mla_step_layer_host(mla_ctx* ctx, uint32_t layer, const void* kv_a_host, const void* q_host,
                         void* out_host, void* stream);
 int mla_step_end(mla_ctx* ctx);

@@ -691,6 +691,16 @@ int mla_merge_partials(mla_ctx* c, uint32_t layer, uint32_t n_parts, uint32_t ro
     return MLA_OK;
 }
 
+static bool is_pinned(const void* p)
+{
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeHost;
+}
+
 int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const void* q_host, void* out_host,
                         void* stream)
 {
@@ -698,24 +708,43 @@ int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layer_host outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     auto st = static_cast<cudaStream_t>(stream);
-    const size_t R = c->cfg.max_rows, H = c->cfg.n_heads, rows = c->meta.rows;
+    const size_t R = c->cfg.max_rows, H = c->cfg.n_heads, rows = c->meta.rows, L = c->cfg.n_layers;
+    const size_t kv_cap = R * mla::kRow * 2, q_cap = R * H * mla::kQDim * 2, o_cap = R * H * mla::kVDim * 2;
     const size_t kv_b = rows * mla::kRow * 2, q_b = rows * H * mla::kQDim * 2, o_b = rows * H * mla::kVDim * 2;
-    if (!c->h_in) {
-        CU_TRY(c, cudaMallocHost(&c->h_in, R * mla::kRow * 2 + R * H * mla::kQDim * 2));
-        CU_TRY(c, cudaMallocHost(&c->h_out, R * H * mla::kVDim * 2));
-        CU_TRY(c, cudaMalloc(&c->d_kv, R * mla::kRow * 2));
-        CU_TRY(c, cudaMalloc(&c->d_q, R * H * mla::kQDim * 2));
-        CU_TRY(c, cudaMalloc(&c->d_out, R * H * mla::kVDim * 2));
+    if (!c->d_kv) {
+        // one device slot per layer: the layers of a step then queue up without waiting for
+        // each other's copies
+        CU_TRY(c, cudaMalloc(&c->d_kv, L * kv_cap));
+        CU_TRY(c, cudaMalloc(&c->d_q, L * q_cap));
+        CU_TRY(c, cudaMalloc(&c->d_out, L * o_cap));
     }
-    // the staging buffers are reused by the next call: drain the stream's earlier use of them
+    char* d_kv = static_cast<char*>(c->d_kv) + layer * kv_cap;
+    char* d_q = static_cast<char*>(c->d_q) + layer * q_cap;
+    char* d_out = static_cast<char*>(c->d_out) + layer * o_cap;
+    const bool direct = is_pinned(kv_a_host) && is_pinned(q_host) && is_pinned(out_host);
+    if (direct) {
+        // page-locked caller buffers: fully asynchronous, the caller synchronises the stream
+        // (or calls mla_status) before reading out_host
+        CU_TRY(c, cudaMemcpyAsync(d_kv, kv_a_host, kv_b, cudaMemcpyHostToDevice, st));
+        CU_TRY(c, cudaMemcpyAsync(d_q, q_host, q_b, cudaMemcpyHostToDevice, st));
+        if (int e = run_append(c, layer, d_kv, st)) return e;
+        if (int e = run_attend(c, layer, d_q, d_out, nullptr, st)) return e;
+        CU_TRY(c, cudaMemcpyAsync(out_host, d_out, o_b, cudaMemcpyDeviceToHost, st));
+        return MLA_OK;
+    }
+    if (!c->h_in) {
+        CU_TRY(c, cudaMallocHost(&c->h_in, kv_cap + q_cap));
+        CU_TRY(c, cudaMallocHost(&c->h_out, o_cap));
+    }
+    // pageable caller buffers: staged through page-locked memory, synchronous
     CU_TRY(c, cudaStreamSynchronize(st));
     std::memcpy(c->h_in, kv_a_host, kv_b);
-    std::memcpy(static_cast<char*>(c->h_in) + R * mla::kRow * 2, q_host, q_b);
-    CU_TRY(c, cudaMemcpyAsync(c->d_kv, c->h_in, kv_b, cudaMemcpyHostToDevice, st));
-    CU_TRY(c, cudaMemcpyAsync(c->d_q, static_cast<char*>(c->h_in) + R * mla::kRow * 2, q_b, cudaMemcpyHostToDevice, st));
-    if (int e = run_append(c, layer, c->d_kv, st)) return e;
-    if (int e = run_attend(c, layer, c->d_q, c->d_out, nullptr, st)) return e;
-    CU_TRY(c, cudaMemcpyAsync(c->h_out, c->d_out, o_b, cudaMemcpyDeviceToHost, st));
+    std::memcpy(static_cast<char*>(c->h_in) + kv_cap, q_host, q_b);
+    CU_TRY(c, cudaMemcpyAsync(d_kv, c->h_in, kv_b, cudaMemcpyHostToDevice, st));
+    CU_TRY(c, cudaMemcpyAsync(d_q, static_cast<char*>(c->h_in) + kv_cap, q_b, cudaMemcpyHostToDevice, st));
+    if (int e = run_append(c, layer, d_kv, st)) return e;
+    if (int e = run_attend(c, layer, d_q, d_out, nullptr, st)) return e;
+    CU_TRY(c, cudaMemcpyAsync(c->h_out, d_out, o_b, cudaMemcpyDeviceToHost, st));
     CU_TRY(c, cudaStreamSynchronize(st));
     std::memcpy(out_host, c->h_out, o_b);
     return MLA_OK;
