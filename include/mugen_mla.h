@@ -199,6 +199,27 @@ int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_be
 int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
                    const void* dev_rows, void* stream);
 
+/* ---- for callers that may not allocate ------------------------------------------------------ */
+/* No counterpart in the reference.  Absorbed MLA attention of one query row over one CONTIGUOUS
+ * latent cache, without a context and without any allocation: no cudaMalloc, cudaFree or
+ * allocating library routine is called, now or later.  For callers whose device memory is owned
+ * by someone else's pool, or that must not trigger cudaMalloc's device-wide synchronisation.
+ * Intermediates live in an 8.2 MiB array built into the library (held on every GPU the process
+ * uses until exit), hence the limits n_heads <= 128 and seq_len <= 65536; larger sizes return
+ * MLA_ERR_CAPACITY.  All pointers are DEVICE pointers in `dtype`:
+ *   q     [n_heads][192]  post-RoPE query (nope first)     out  [n_heads][128]
+ *   cache [seq_len rounded up to a multiple of 64][576]   rows past seq_len are read, never used:
+ *                                                         they must be mapped and hold finite values
+ *   w_uk, w_uv  (n_heads*128) x 512 row-major, as the reference keeps them (transformer.cpp:3178-3221)
+ * The first call on a device resolves the array's address (cudaGetSymbolAddress) and sets a
+ * kernel attribute; make it before any stream capture.  Calls that overlap on one GPU race on
+ * the shared array: serialise them.  Asynchronous on `stream`.  mla_noalloc_last_error() gives
+ * the text of the calling thread's last failure. */
+int mla_attention_noalloc(uint32_t dtype, uint32_t n_heads, uint32_t seq_len, const void* q,
+                          const void* cache, const void* w_uk, const void* w_uv, void* out,
+                          void* stream);
+const char* mla_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

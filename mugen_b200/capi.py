@@ -63,6 +63,8 @@ SIGNATURES = {
     "mla_profile_read": (C.c_int, [vp, C.POINTER(u32), C.POINTER(f32)]),
     "mla_read_rows": (C.c_int, [vp, u32, u32, u32, u32, vp, vp]),
     "mla_write_rows": (C.c_int, [vp, u32, u32, u32, u32, vp, vp]),
+    "mla_attention_noalloc": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, vp, vp]),
+    "mla_noalloc_last_error": (C.c_char_p, []),
 }
 
 _lib = None
