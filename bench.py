@@ -242,9 +242,7 @@ def run_ours(a):
 
     def one_step():
         ctx.step_begin(seqs)
-        for l in range(L):
-            ctx.step_append(l, kv[l])
-            ctx.step_attend(l, q[l], out[l])
+        ctx.step_layers(0, L, kv, q, out)      # per layer: append, absorb, split-KV attention, merge + W_UV
         ctx.step_end()
 
     for _ in range(a.warmup):

@@ -155,6 +155,12 @@ int mla_step_begin(mla_ctx* ctx, uint32_t n_seq, const uint32_t* seq_ids, const 
 int mla_step_append(mla_ctx* ctx, uint32_t layer, const void* kv_a, void* stream);
 /* q: DEVICE [rows][n_heads][192]; out: DEVICE [rows][n_heads][128]. */
 int mla_step_attend(mla_ctx* ctx, uint32_t layer, const void* q, void* out, void* stream);
+/* append + attend for `n_layers` consecutive layers in one call (an attention stack with nothing
+ * between its layers, or a caller that has all layers' inputs ready): kv_a DEVICE
+ * [n_layers][rows][576], q DEVICE [n_layers][rows][n_heads][192], out DEVICE
+ * [n_layers][rows][n_heads][128].  Same kernels and order as the per-layer calls. */
+int mla_step_layers(mla_ctx* ctx, uint32_t layer_begin, uint32_t n_layers, const void* kv_a,
+                    const void* q, void* out, void* stream);
 /* Same two calls with HOST buffers: copies kv_a and q in, runs append + attend, copies out
  * back, all on `stream`.  Page-locked caller buffers are copied directly and the call returns
  * without waiting (synchronise the stream, or call mla_status, before reading out_host);

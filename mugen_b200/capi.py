@@ -52,6 +52,7 @@ SIGNATURES = {
     "mla_step_begin": (C.c_int, [vp, u32, vp, vp, vp]),
     "mla_step_append": (C.c_int, [vp, u32, vp, vp]),
     "mla_step_attend": (C.c_int, [vp, u32, vp, vp, vp]),
+    "mla_step_layers": (C.c_int, [vp, u32, u32, vp, vp, vp, vp]),
     "mla_step_layer_host": (C.c_int, [vp, u32, vp, vp, vp, vp]),
     "mla_step_end": (C.c_int, [vp]),
     "mla_step_info": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32)]),

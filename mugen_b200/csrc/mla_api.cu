@@ -671,6 +671,26 @@ int mla_step_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, void* 
     return run_attend(c, layer, q, out, nullptr, static_cast<cudaStream_t>(stream));
 }
 
+int mla_step_layers(mla_ctx* c, uint32_t layer_begin, uint32_t n_layers, const void* kv_a, const void* q, void* out,
+                    void* stream)
+{
+    if (!c || !kv_a || !q || !out) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layers outside step_begin/step_end");
+    if (uint64_t(layer_begin) + n_layers > c->cfg.n_layers) return fail(c, MLA_ERR_INVALID, "layer range out of bounds");
+    auto st = static_cast<cudaStream_t>(stream);
+    const size_t rows = c->meta.rows, H = c->cfg.n_heads;
+    const size_t kv_b = rows * mla::kRow * 2, q_b = rows * H * mla::kQDim * 2, o_b = rows * H * mla::kVDim * 2;
+    for (uint32_t i = 0; i < n_layers; i++) {
+        const uint32_t layer = layer_begin + i;
+        if (int e = check_layer(c, layer, true)) return e;
+        if (int e = run_append(c, layer, static_cast<const char*>(kv_a) + i * kv_b, st)) return e;
+        if (int e = run_attend(c, layer, static_cast<const char*>(q) + i * q_b, static_cast<char*>(out) + i * o_b,
+                               nullptr, st))
+            return e;
+    }
+    return MLA_OK;
+}
+
 int mla_step_attend_partial(mla_ctx* c, uint32_t layer, const void* q, float* partial, void* stream)
 {
     if (!c || !q || !partial) return fail(c, MLA_ERR_INVALID, "null argument");

@@ -14,7 +14,7 @@ namespace mla {
 //   k[i]    = T( x0*cos - x1*sin ),  k[i+32] = T( x1*cos + x0*sin )   from the original x0, x1
 // cos/sin come from a host-built table (the host evaluates them with the same libm calls as
 // the CPU path; device cosf/sinf are not bit-identical to glibc's).
-// One block per row; thread 0 owns the sequential sum, warp 1 does the rotation meanwhile.
+// One block per row; the squares are formed in parallel, thread 0 adds them in order.
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -25,6 +25,7 @@ append_kernel(const T* __restrict__ kv_a, T* __restrict__ pool, uint64_t pool_sl
 {
     __shared__ __align__(16) T xin[kRow];
     __shared__ __align__(16) T xout[kRow];
+    __shared__ float sq[kRank];
     __shared__ float rinv_s;
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
     const uint64_t slot = row_slot[r];
@@ -39,15 +40,13 @@ append_kernel(const T* __restrict__ kv_a, T* __restrict__ pool, uint64_t pool_sl
         reinterpret_cast<uint4*>(xin)[tid] =
             reinterpret_cast<const uint4*>(kv_a + size_t(r) * kRow)[tid];
     __syncthreads();
-    if (tid == 0) {
-        float ss = 0.0f;
-#pragma unroll 8
-        for (int i = 0; i < kRank; i++) {
-            const float v = Elem<T>::to_f32(xin[i]);
-            ss = __fadd_rn(ss, __fmul_rn(v, v));
-        }
-        rinv_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(kRank)), eps)));
-    } else if (tid >= 32 && tid < 64) {
+    // squares in parallel (each product is rounded on its own, as in the reference), then ONE
+    // thread adds them in index order: the sum's rounding sequence is the reference's
+    for (int i = tid; i < kRank; i += 128) {
+        const float v = Elem<T>::to_f32(xin[i]);
+        sq[i] = __fmul_rn(v, v);
+    }
+    if (tid >= 32 && tid < 64) {
         const int i = tid - 32;
         const float c = cos_sin[size_t(pos) * kRope + i];
         const float s = cos_sin[size_t(pos) * kRope + 32 + i];
@@ -55,6 +54,13 @@ append_kernel(const T* __restrict__ kv_a, T* __restrict__ pool, uint64_t pool_sl
         const float x1 = Elem<T>::to_f32(xin[kRank + 32 + i]);
         xout[kRank + i]      = Elem<T>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
         xout[kRank + 32 + i] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s)));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float ss = 0.0f;
+#pragma unroll 16
+        for (int i = 0; i < kRank; i++) ss = __fadd_rn(ss, sq[i]);
+        rinv_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(kRank)), eps)));
     }
     __syncthreads();
     const float rinv = rinv_s;

@@ -143,6 +143,11 @@ class MlaContext:
     def step_attend(self, layer: int, q, out) -> None:
         self._check(self.lib.mla_step_attend(self.h, layer, self._dev(q), self._dev(out), self._stream()))
 
+    def step_layers(self, layer_begin: int, n_layers: int, kv_a, q, out) -> None:
+        """append + attend for consecutive layers in one call; tensors are [n_layers][rows]..."""
+        self._check(self.lib.mla_step_layers(self.h, layer_begin, n_layers, self._dev(kv_a), self._dev(q),
+                                             self._dev(out), self._stream()))
+
     def step_layer_host(self, layer: int, kv_a_host, q_host, out_host) -> None:
         """kv_a_host / q_host / out_host: host torch tensors or numpy arrays (contiguous)."""
         def hp(x):

@@ -264,6 +264,40 @@ def test_decode_steps_multi_layer(torch, oracle, kernel, dt):
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
+def test_step_layers_equals_per_layer_calls(torch, kernel):
+    """The multi-layer call is the same kernels in the same order: bit-identical outputs and rows."""
+    H, L, dt, lens = 64, 3, synth.DT_BF16, [200, 65]
+    case = synth.make_layer_case(333, H, [n + 1 for n in lens], dt)
+    rng = np.random.default_rng(4)
+    kv = _dev(torch, synth.to_bits(rng.standard_normal((L, 2, 576), np.float32), dt))
+    q = _dev(torch, synth.to_bits(rng.standard_normal((L, 2, H, 192), np.float32) * np.float32(0.9), dt))
+    outs, rows = [], []
+    for mode in (0, 1):
+        ctx = make_ctx(case, kernel, n_layers=L)
+        seqs = []
+        for b, n in enumerate(lens):
+            s_ = ctx.seq_create()
+            for l in range(L):
+                ctx.write_rows(l, s_, 0, _dev(torch, case.caches[b][:n]))
+            ctx.advance_seq_len(s_, n)
+            seqs.append(s_)
+        out = torch.zeros((L, 2, H, 128), dtype=torch.int16, device="cuda")
+        ctx.step_begin(seqs)
+        if mode == 0:
+            for l in range(L):
+                ctx.step_append(l, kv[l])
+                ctx.step_attend(l, q[l], out[l])
+        else:
+            ctx.step_layers(0, L, kv, q, out)
+        ctx.step_end()
+        outs.append(_host(out).copy())
+        rows.append(np.stack([ctx.read_rows(l, seqs[0], lens[0], 1) for l in range(L)]))
+        assert ctx.status() == 0
+        ctx.close()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(rows[0], rows[1])
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_prefill_chunk_is_causal(torch, oracle, kernel):
     """A 70-token chunk appended at start_position 50 next to a plain decode row: token t attends
     [0, start+t+1) (transformer.cpp:1325-1337)."""
