@@ -60,7 +60,7 @@ struct mla_ctx {
     uint32_t max_segs = 0;
     uint32_t workers = 1;
     uint32_t* status_dev = nullptr;
-    alignas(64) CUtensorMap tmaps[2];   // tcgen05 path: [0] cache pool, [1] absorbed queries
+    alignas(64) CUtensorMap tmaps[3];   // tcgen05 paths: [0] cache pool (64-token box), [1] absorbed queries, [2] cache pool (32-token box)
 
     // metadata upload ring
     MetaBuf ring[kMetaRing];
@@ -309,7 +309,9 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     int e;
     const bool timed = c->profiling && c->prof_used < c->prof_events.size();
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
-    if (c->kernel == MLA_KERNEL_TCGEN05)
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR)
+        e = mla::launch_decode_tc5_pair(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
+    else if (c->kernel == MLA_KERNEL_TCGEN05)
         e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmaps, layer, c->cfg.n_pages, m,
                                    c->recs, H, c->status_dev, st);
     else
@@ -351,6 +353,17 @@ int make_tensor_maps(mla_ctx* c)
         if (r != CUDA_SUCCESS)
             return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool) failed with code " + std::to_string(int(r)));
     }
+    {   // the same pool with a 32-token box, for the SM-pair kernel (each block stages half a page of K)
+        const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
+        const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
+        const cuuint32_t box[3] = {64, 32, 1};
+        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[2], dt, 3, c->pool, dims, strides, box, estr,
+                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool, half page) failed with code " + std::to_string(int(r)));
+    }
     {   // absorbed queries [max_rows * heads][576]; box = 64 values x 64 head rows
         const cuuint64_t dims[2] = {cuuint64_t(mla::kRow), cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64};
         const cuuint64_t strides[1] = {cuuint64_t(mla::kRow) * 2};
@@ -384,7 +397,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (cfg->page_tokens != 64) return fail(nullptr, MLA_ERR_UNSUPPORTED, "page_tokens must be 64");
     if (cfg->n_pages == 0 || cfg->max_seqs == 0) return fail(nullptr, MLA_ERR_INVALID, "n_pages and max_seqs must be > 0");
     if (cfg->dtype > MLA_DTYPE_BF16) return fail(nullptr, MLA_ERR_INVALID, "dtype must be MLA_DTYPE_F16 or MLA_DTYPE_BF16");
-    if (cfg->kernel > MLA_KERNEL_TCGEN05) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
+    if (cfg->kernel > MLA_KERNEL_TCGEN05_PAIR) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
 
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
@@ -416,7 +429,8 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     // wide head counts fill the 64-row tcgen05 tiles; narrow ones map 1:1 onto m16n8k16
     c->kernel = cfg->kernel == MLA_KERNEL_AUTO ? (cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA) : cfg->kernel;
     const uint32_t H = cfg->n_heads;
-    if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
+    else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
     else c->workers = std::max<uint32_t>(1, c->sm_count * 2 / ((H + 15) / 16));
 
     c->pt = std::make_unique<PageTable>(cfg->page_tokens, cfg->n_pages, cfg->max_seqs, cfg->max_seq_len);
@@ -452,6 +466,13 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     for (auto& mb : c->ring) {
         CR_TRY(cudaMallocHost(&mb.host, c->meta_cap));
         CR_TRY(cudaEventCreateWithFlags(&mb.done, cudaEventDisableTiming));
+    }
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR) {
+        if (int rc = make_tensor_maps(cp)) return bail(rc);
+        if (int ce = mla::decode_tc5_pair_configure()) {
+            cp->err = std::string("tcgen05 pair kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+            return bail(MLA_ERR_CUDA);
+        }
     }
     if (c->kernel == MLA_KERNEL_TCGEN05) {
         if (int rc = make_tensor_maps(cp)) return bail(rc);
@@ -828,7 +849,7 @@ int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
 const char* mla_kernel_name(const mla_ctx* c)
 {
     if (!c) return "";
-    return c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
+    return c->kernel == MLA_KERNEL_TCGEN05_PAIR ? "tcgen05-pair" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
 }
 
 int mla_read_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, void* host_out, void* stream)

@@ -1,0 +1,636 @@
+// Split-KV absorbed MLA attention for 128-head groups on a PAIR of SMs (thread-block cluster of 2,
+// tcgen05.mma.cta_group::2), sm_100a.
+//
+// The single-block kernel (mla_decode_tc5.cu) is limited by the shared-memory operand feed of
+// the tensor core: per 64-token tile its MMAs read 245 KB.  Here the two blocks of a cluster take
+// 64 heads each and issue pair MMAs, in which the B operand is split between the two blocks'
+// shared memories and broadcast by the hardware:
+//
+//   QK   S[128 heads x 64 tok] = Q' . K^T     M=128 (64 rows per block), N=64 (32 tokens per block)
+//        A = the block's own Q'[64 x 576], B = the block's own HALF of the tile's tokens
+//   PV   O^T[512 dims x 128 heads] += V^T . P^T     M=256 (128 dims per block) x 2, N=128, K=16
+//        A = the block's own dims of V^T (MN-major), B = the block's own 64 heads of P
+//
+// so a block stages per tile only K[32 tok x 576] + V[64 tok x 256 dims] (69.6 KB) and its MMAs read
+// 160 KB instead of 245 KB.  Each block keeps O^T for ITS 256 latent dims and ALL 128 heads
+// (2 x 128 TMEM columns), the scores of ITS 64 heads (4 partial tiles x 32 columns), and runs the
+// softmax of its heads.  Only block 0 of the pair issues MMAs (6 issuer warps, as in the
+// single-block kernel); completion is multicast to both blocks' mbarriers with tcgen05.commit.
+// TMA loads carry no multicast: every block fetches its own boxes, and signals block 0's barrier.
+//
+// Softmax: the reference maximum of a head moves only when a tile exceeds it by 2^8 (or at the
+// first tile of a segment).  A tile on which no head of the pair needs that is the common case
+// and costs one cluster-wide mbarrier round; otherwise the blocks exchange maxima and scale
+// factors through distributed shared memory and both rescale their O^T columns.
+//
+// Every wait on an mbarrier is bounded (about 2 s), raises ST_WAIT_TIMEOUT and lets all roles leave.
+#include <cuda.h>
+
+#include "mla_launch.h"
+
+namespace mla {
+
+namespace {
+
+constexpr int TILE = 64;
+constexpr int HG = 64;                              // heads per block (128 per pair)
+constexpr int NSUB = kRow / 64;                     // 9
+constexpr int KSUB_BYTES = 32 * 128;                // K sub-tile: 32 own tokens x 64 dims
+constexpr int VSUB_BYTES = 64 * 128;                // V sub-tile: 64 tokens x 64 dims
+constexpr int K_BYTES = NSUB * KSUB_BYTES;          // 36,864
+constexpr int V_BYTES = 4 * VSUB_BYTES;             // 32,768: the block's 256 latent dims
+constexpr int STAGE_BYTES = K_BYTES + V_BYTES;      // 69,632
+constexpr int KV_STAGES = 2;
+constexpr int Q_BYTES = NSUB * HG * 128;            // 73,728
+constexpr int P_BYTES = HG * 128;                   // 8,192
+constexpr int OFF_Q = 0;
+constexpr int OFF_ST = OFF_Q + Q_BYTES;
+constexpr int OFF_P = OFF_ST + KV_STAGES * STAGE_BYTES;
+constexpr int OFF_MISC = OFF_P + P_BYTES;
+constexpr int MISC_BYTES = 3072;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+
+// misc area layout (bytes from OFF_MISC)
+constexpr int M_BAR = 0;          // mbarriers, 8 B each
+constexpr int M_TMEM = 256;       // tmem base
+constexpr int M_ABORT = 260;
+constexpr int M_FLAG = 264;       // [2] "some head of the pair must move its maximum", by tile parity
+constexpr int M_ALPHA = 512;      // [2][128] floats: scale factor per head of the pair, by tile parity
+constexpr int M_HMAX = 1536;      // [2][64] floats: tile maximum of each token half per head
+constexpr int M_LSUM = 2048;      // [64] floats: second half's partial sum at the epilogue
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
+constexpr uint32_t COL_S = 256;     // 4 partial score tiles x 32 columns
+
+constexpr int N_QK = 4, N_PV = 2;
+constexpr int NUM_THREADS = 32 * (1 + N_QK + N_PV + 4);
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int PAIR_SOFTMAX_THREADS = 256;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+constexpr int PREFETCH_TILES = 4;
+
+enum { B_QFULL = 0, B_QEMPTY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_SEMPTY, B_PFULL, B_PEMPTY,
+       B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this block) in block `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+// ---- mbarrier ------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---- TMA (no multicast; .cta_group::2 only lets the completion land on the pair leader's barrier)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// ---- tcgen05, cta_group::2 -----------------------------------------------------------------
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// completion of all MMAs issued so far by this thread -> the barrier at this offset in BOTH blocks
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar), "h"(uint16_t(3)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// shared-memory matrix descriptor halves (128-byte swizzle, version 1); see mla_decode_tc5.cu
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+struct SegInfo {
+    uint32_t row, page_begin, n_tiles, n_tok;
+};
+__device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
+    SegInfo s;
+    s.row = m.seg_row[seg];
+    s.page_begin = m.seg_page_begin[seg];
+    const uint32_t pe = m.seg_page_end[seg];
+    const uint32_t len = m.row_len[s.row];
+    const uint32_t tb = s.page_begin * kPage, te = min(len, pe * kPage);
+    s.n_tok = te > tb ? te - tb : 0;
+    s.n_tiles = (s.n_tok + TILE - 1) / TILE;
+    return s;
+}
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_q,
+                       uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
+                       float scale_log2, uint32_t* __restrict__ status)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* sm = smem_raw + (base - raw);
+    const uint32_t sQ = base + OFF_Q, sST = base + OFF_ST, sP = base + OFF_P;
+    const uint32_t sBar = base + OFF_MISC + M_BAR;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_ABORT);
+    volatile uint32_t* need_flag = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC + M_FLAG);
+    float* alpha_all = reinterpret_cast<float*>(sm + OFF_MISC + M_ALPHA);
+    float* half_max = reinterpret_cast<float*>(sm + OFF_MISC + M_HMAX);
+    float* l_other = reinterpret_cast<float*>(sm + OFF_MISC + M_LSUM);
+    auto bar = [&](int i) { return sBar + 8u * uint32_t(i); };
+
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t rank = cluster_rank();                 // 0 = pair leader (issues the MMAs)
+    const uint32_t worker = blockIdx.x / 2;
+    const uint32_t hpair = blockIdx.y * (2 * HG);        // first head of the pair's 128
+    const uint32_t h0 = hpair + rank * HG;               // first head of this block's 64
+    const uint32_t seg_begin = m.cta_seg_begin[worker], seg_end = m.cta_seg_begin[worker + 1];
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        need_flag[0] = need_flag[1] = 0;
+        mbar_init(bar(B_QFULL), 1);
+        mbar_init(bar(B_QEMPTY), N_QK);
+        mbar_init(bar(B_KVFULL0), 1);
+        mbar_init(bar(B_KVFULL1), 1);
+        mbar_init(bar(B_KVEMPTY0), N_PV);
+        mbar_init(bar(B_KVEMPTY1), N_PV);
+        mbar_init(bar(B_SFULL), N_QK);
+        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_PFULL), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_PEMPTY), N_PV);
+        mbar_init(bar(B_OFULL), N_PV);
+        mbar_init(bar(B_SYNCA0), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_SYNCA1), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_SYNCB0), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_SYNCB1), PAIR_SOFTMAX_THREADS);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    // both blocks' barriers must exist before either sends a remote arrive or a TMA completion
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    tc_fence_after();
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+    if (warp == 0) {
+        // ===================== TMA producer (each block fetches its own boxes) =====================
+        if (lane == 0) {
+            const uint32_t leader_qfull = map_to_rank(bar(B_QFULL), 0);
+            const uint32_t leader_kvfull[2] = {map_to_rank(bar(B_KVFULL0), 0), map_to_rank(bar(B_KVFULL1), 0)};
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                ok = mbar_wait(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
+                if (!ok) break;
+                if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
+                for (int j = 0; j < NSUB; j++)
+                    tma_load_2d_pair(sQ + j * (HG * 128), &map_q, leader_qfull, j * 64, int(s.row * H + h0));
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
+                auto prefetch_tile = [&](uint32_t jj) {
+                    const uint32_t pg = tbl[s.page_begin + jj];
+                    if (pg < n_pages)
+                        for (int c = 0; c < NSUB; c++)
+                            tma_prefetch_3d(&map_kv, c * 64, int(pg * kPage + 32 * rank), int(layer));
+                };
+                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
+                for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                    const uint32_t st = t % KV_STAGES;
+                    if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
+                    ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+                    if (!ok) break;
+                    uint32_t page = tbl[s.page_begin + j];
+                    if (page >= n_pages) {
+                        atomicOr(status, ST_BAD_PAGE);
+                        page = 0;
+                    }
+                    if (rank == 0) mbar_expect_tx(bar(B_KVFULL0 + st), 2 * STAGE_BYTES);
+                    const uint32_t dst = sST + st * STAGE_BYTES;
+                    const int slot0 = int(page * kPage);
+                    // K: this block's 32 tokens, all 576 dims
+                    for (int c = 0; c < NSUB; c++)
+                        tma_load_3d_pair(dst + c * KSUB_BYTES, &map_kv, leader_kvfull[st], c * 64, slot0 + 32 * int(rank),
+                                         int(layer));
+                    // V: all 64 tokens, this block's 256 latent dims = sub-tiles 4c+2r, 4c+2r+1 (c = 0, 1)
+                    for (int v = 0; v < 4; v++) {
+                        const int sub = 4 * (v / 2) + 2 * int(rank) + (v % 2);
+                        for (int hf = 0; hf < 2; hf++)
+                            tma_load_3d_pair(dst + K_BYTES + v * VSUB_BYTES + hf * (VSUB_BYTES / 2), &map_kv,
+                                             leader_kvfull[st], sub * 64, slot0 + 32 * hf, int(layer));
+                    }
+                }
+                nseg++;
+            }
+        }
+    } else if (warp <= N_QK + N_PV) {
+        // ===================== MMA issuers (pair leader only) =====================
+        if (rank == 0) {
+            constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 128, TILE, 0, 0);        // 64 head rows per block
+            constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 256, 2 * HG, 1, 0);      // 128 dims per block
+            constexpr uint32_t HI = desc_hi(1024);
+            const bool is_qk = warp <= N_QK;
+            const uint32_t part = is_qk ? warp - 1 : warp - 1 - N_QK;
+            const int c_lo = part == 0 ? 0 : 1 + 2 * int(part), c_hi = 3 + 2 * int(part);
+            const uint32_t qk_a = desc_lo(sQ, 16);
+            const uint32_t k0 = desc_lo(sST, 16), k1 = desc_lo(sST + STAGE_BYTES, 16);
+            const uint32_t v0 = desc_lo(sST + K_BYTES, VSUB_BYTES), v1 = desc_lo(sST + STAGE_BYTES + K_BYTES, VSUB_BYTES);
+            const uint32_t pv_b = desc_lo(sP, 16);
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                    const uint32_t st = t % KV_STAGES;
+                    if (is_qk) {
+                        ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
+                             mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t b0 = st ? k1 : k0;
+                        const uint32_t d = tmem + COL_S + part * (TILE / 2);
+                        if (elect_one()) {
+#pragma unroll
+                            for (int c = 0; c < NSUB; c++) {
+                                if (c >= c_lo && c < c_hi) {
+#pragma unroll
+                                    for (int k = 0; k < 4; k++)
+                                        tc_mma_pair(d, qk_a + ((c * (HG * 128) + k * 32) >> 4), HI,
+                                                    b0 + ((c * KSUB_BYTES + k * 32) >> 4), HI, IDESC_QK,
+                                                    (c == c_lo && k == 0) ? 0u : 1u);
+                                }
+                            }
+                            tc_commit_pair(bar(B_SFULL));
+                            if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
+                        }
+                        __syncwarp();
+                    } else {
+                        ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t a0 = (st ? v1 : v0) + ((part * 2 * VSUB_BYTES) >> 4);   // chunk `part`
+                        const uint32_t fresh = j == 0 ? 0u : 1u;
+                        if (elect_one()) {
+#pragma unroll
+                            for (int k = 0; k < TILE / 16; k++)
+                                tc_mma_pair(tmem + COL_O + part * (2 * HG), a0 + ((k * 2048) >> 4), HI, pv_b + ((k * 32) >> 4),
+                                            HI, IDESC_PV, k == 0 ? fresh : 1u);
+                            tc_commit_pair(bar(B_KVEMPTY0 + st));
+                            tc_commit_pair(bar(B_PEMPTY));
+                            if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_OFULL));
+                        }
+                        __syncwarp();
+                    }
+                }
+                nseg++;
+            }
+        }
+    } else {
+        // ===================== softmax / correction / epilogue (both blocks) =====================
+        // S of a pair MMA with 64 rows per block: head row r sits in TMEM lane r (tokens 0-31 of
+        // the tile) and lane 64+r (tokens 32-63).  Thread = one lane: (head, token half).
+        const uint32_t q4 = warp % 4;
+        const uint32_t lane_base = (q4 * 32u) << 16;
+        const uint32_t half = q4 / 2;                         // which 32 tokens of the tile
+        const uint32_t hl = 32 * (q4 % 2) + lane;             // head within this block's 64
+        const uint32_t st_id = tid - (NUM_THREADS - SOFTMAX_THREADS);
+        const uint32_t peer = rank ^ 1;
+        // remote twins of the barriers and scratch words this thread signals
+        const uint32_t r_sempty = map_to_rank(bar(B_SEMPTY), 0), r_pfull = map_to_rank(bar(B_PFULL), 0);
+        const uint32_t r_synca[2] = {map_to_rank(bar(B_SYNCA0), peer), map_to_rank(bar(B_SYNCA1), peer)};
+        const uint32_t r_syncb[2] = {map_to_rank(bar(B_SYNCB0), peer), map_to_rank(bar(B_SYNCB1), peer)};
+        const uint32_t r_flag = map_to_rank(base + OFF_MISC + M_FLAG, peer);
+        const uint32_t r_alpha = map_to_rank(base + OFF_MISC + M_ALPHA, peer);
+        float m_used = -INFINITY, l_part = 0.0f;
+        uint32_t t = 0, nseg = 0, nb[2] = {0, 0};             // nb: uses of SYNCB[par] so far
+        bool fail = false;
+        auto wait_w = [&](uint32_t b, uint32_t parity) {
+            if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
+            fail = __any_sync(0xffffffffu, fail);
+        };
+        auto group_or = [&](bool pred) -> bool {              // barrier over this block's 128 threads + OR
+            uint32_t r;
+            asm volatile(
+                "{\n.reg .pred pi, po;\n"
+                "setp.ne.b32 pi, %1, 0;\n"
+                "barrier.cta.red.or.pred po, 1, 128, pi;\n"
+                "selp.u32 %0, 1, 0, po;\n}\n"
+                : "=r"(r) : "r"(uint32_t(pred)) : "memory");
+            return r != 0;
+        };
+        bool stop = false;
+        for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
+            const SegInfo s = load_seg(m, seg);
+            if (s.n_tiles == 0) {
+                // nothing to attend: each block writes its 256 dims of every head, and (m, l) of its own heads
+                for (uint32_t h = 0; h < 2 * HG; h++) {
+                    if (hpair + h >= H) break;
+                    float* rc = recs + (size_t(seg) * H + hpair + h) * kPart;
+                    for (uint32_t d = st_id; d < 256; d += SOFTMAX_THREADS) {
+                        const uint32_t dim = (d / 128) * 256 + rank * 128 + (d % 128);
+                        rc[2 + dim] = 0.0f;
+                    }
+                    if (st_id == 0 && h / HG == rank) { rc[0] = -INFINITY; rc[1] = 0.0f; }
+                }
+                continue;
+            }
+            m_used = -INFINITY;
+            l_part = 0.0f;
+            for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                const uint32_t par = t & 1;
+                wait_w(bar(B_SFULL), t & 1);
+                uint32_t sv[32];
+                if (!fail) {
+                    tc_fence_after();
+                    uint32_t sw[32];
+                    tc_ld32(tmem + lane_base + COL_S, sv);
+                    tc_ld32(tmem + lane_base + COL_S + 32, sw);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    tc_ld32(tmem + lane_base + COL_S + 64, sw);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    tc_ld32(tmem + lane_base + COL_S + 96, sw);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    tc_fence_before();
+                    if (rank == 0) mbar_arrive_local(bar(B_SEMPTY));
+                    else mbar_arrive_cluster(r_sempty);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = 0u;
+                }
+                const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float v = __uint_as_float(sv[i]) * scale_log2;
+                    v = (half * 32 + uint32_t(i) < valid) ? v : -INFINITY;
+                    sv[i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+                // does any head of the pair have to move its reference maximum on this tile?
+                const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
+                if (need && !fail) {
+                    atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
+                    asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
+                }
+                // cluster-wide round A: every softmax thread of the pair has posted its flag
+                if (!fail) {
+                    mbar_arrive_local(bar(B_SYNCA0 + par));
+                    mbar_arrive_cluster(r_synca[par]);
+                }
+                wait_w(bar(B_SYNCA0 + par), (t >> 1) & 1);
+                if (group_or(fail)) { stop = true; break; }
+                const bool slow = need_flag[par] != 0;
+                float alpha = 1.0f;
+                if (slow) {
+                    // exchange the two halves' maxima inside the block, decide per head, publish the
+                    // scale factors to both blocks
+                    half_max[half * HG + hl] = mx;
+                    group_or(false);
+                    const float mrow = fmaxf(half_max[hl], half_max[HG + hl]);
+                    if (j == 0) { m_used = mrow; alpha = 0.0f; }
+                    else if (mrow > m_used + RESCALE_THRESHOLD) { alpha = fast_ex2(m_used - mrow); m_used = mrow; }
+                    if (half == 0) {
+                        alpha_all[par * 128 + rank * HG + hl] = alpha;
+                        asm volatile("st.relaxed.cluster.shared::cluster.f32 [%0], %1;\n"
+                                     ::"r"(r_alpha + 4 * (par * 128 + rank * HG + hl)), "f"(alpha) : "memory");
+                    }
+                    mbar_arrive_local(bar(B_SYNCB0 + par));
+                    mbar_arrive_cluster(r_syncb[par]);
+                    wait_w(bar(B_SYNCB0 + par), nb[par] & 1);
+                    nb[par]++;
+                    l_part *= alpha;
+                }
+                float sum = 0.0f;
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
+                    const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                    sum += p0 + p1;
+                    pk[i / 2] = Elem<T>::pack2(p0, p1);
+                }
+                l_part += sum;
+                // PV of the previous tile must be complete: O is stable and P is free
+                wait_w(bar(B_PEMPTY), (t - 1) & 1);
+                if (fail) continue;            // carried to the next barrier
+                tc_fence_after();
+                if (slow && j > 0) {
+                    // O^T[this block's dims][128 heads] *= alpha[head], both chunks
+#pragma unroll 1
+                    for (int c = 0; c < 8; c++) {
+                        uint32_t o[32];
+                        const uint32_t col = COL_O + c * 32;
+                        tc_ld32(tmem + lane_base + col, o);
+                        tc_wait_ld();
+                        const float* al = alpha_all + par * 128 + (c & 3) * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * al[i]);
+                        tc_st32(tmem + lane_base + col, o);
+                    }
+                    tc_wait_st();
+                }
+                {
+                    // row hl of the K-major swizzled P tile, this thread's 32 tokens = chunks 4*half .. +3
+                    unsigned char* prow = sm + OFF_P + hl * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                        *reinterpret_cast<uint4*>(prow + (((4 * half + ch) ^ (hl & 7)) << 4)) = v;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                tc_fence_before();
+                if (rank == 0) mbar_arrive_local(bar(B_PFULL));
+                else mbar_arrive_cluster(r_pfull);
+                // the flag of this parity is next written two tiles from now: clear it once every
+                // thread of the block has read it (they all passed round A of this tile)
+                if (st_id == 0 && slow) need_flag[par] = 0;
+            }
+            if (stop) break;
+            // ---- epilogue: O^T (this block's 256 dims x 128 heads) -> acc[head][dim]; (m, l) of own heads
+            wait_w(bar(B_OFULL), nseg & 1);
+            if (half == 1) l_other[hl] = l_part;
+            if (group_or(fail)) { stop = true; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 8; c++) {
+                uint32_t o[32];
+                tc_ld32(tmem + lane_base + COL_O + c * 32, o);
+                tc_wait_ld();
+                const uint32_t dim = (c / 4) * 256 + rank * 128 + q4 * 32 + lane;
+                const uint32_t hb = hpair + (c & 3) * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (hb + i < H) recs[(size_t(seg) * H + hb + i) * kPart + 2 + dim] = __uint_as_float(o[i]);
+                }
+            }
+            if (half == 0 && h0 + hl < H) {
+                float* rc = recs + (size_t(seg) * H + h0 + hl) * kPart;
+                rc[0] = m_used;
+                rc[1] = l_part + l_other[hl];
+            }
+            tc_fence_before();
+            group_or(false);                   // l_other is reused by the next segment
+            nseg++;
+        }
+    }
+
+    // Neither block may leave while its twin can still signal its barriers, write its scratch or
+    // feed a pair MMA from its shared memory.
+    tc_fence_before();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+}  // namespace
+
+int decode_tc5_pair_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(decode_tc5_pair_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(decode_tc5_pair_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES);
+    return int(e);
+}
+
+// tmaps: [1] absorbed queries (box 64 x 64), [2] cache pool with a 64-value x 32-token box.
+int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
+                           float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
+{
+    if (m.ctas == 0) return 0;
+    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);
+    const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
+    dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
+    if (dtype == 0)
+        decode_tc5_pair_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[1], layer, n_pages, m, recs,
+                                                                             H, scale_log2, status);
+    else
+        decode_tc5_pair_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[1], layer, n_pages, m,
+                                                                                    recs, H, scale_log2, status);
+    return int(cudaGetLastError());
+}
+
+}  // namespace mla

@@ -30,6 +30,12 @@ int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t 
                       cudaStream_t st);
 int decode_tc5_configure();   // sets the kernel's shared-memory attribute once
 
+// The same on a pair of SMs (cluster of 2, tcgen05.mma.cta_group::2): grid (2 x persistent pairs,
+// ceil(H/128)).  tmaps: [1] absorbed queries, [2] the pool with a 32-token box.
+int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
+                           float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
+int decode_tc5_pair_configure();
+
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
                   cudaStream_t st);
