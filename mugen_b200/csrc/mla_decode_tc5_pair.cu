@@ -25,6 +25,9 @@
 //
 // Every wait on an mbarrier is bounded (about 2 s), raises ST_WAIT_TIMEOUT and lets all roles leave.
 #include <cuda.h>
+#ifdef MLA_TC5_TRACE
+#include <cstdio>
+#endif
 
 #include "mla_launch.h"
 
@@ -61,12 +64,12 @@ constexpr int M_LSUM = 2048;      // [64] floats: second half's partial sum at t
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
-constexpr uint32_t COL_S = 256;     // 4 partial score tiles x 32 columns
+constexpr uint32_t COL_S = 256;     // N_QK partial score tiles x 32 columns
 
-constexpr int N_QK = 4, N_PV = 2;
+constexpr int N_QK = 2, N_PV = 2;                   // pair MMAs issue quickly: two issuers each suffice
 constexpr int NUM_THREADS = 32 * (1 + N_QK + N_PV + 4);
 constexpr int SOFTMAX_THREADS = 128;
-constexpr int PAIR_SOFTMAX_THREADS = 256;
+constexpr int PAIR_SOFTMAX_WARPS = 8;               // barriers fed by the softmax role count warps, not threads
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 constexpr int PREFETCH_TILES = 4;
@@ -96,6 +99,42 @@ __device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// default semantics (release at block scope) on the twin block's barrier: what orders this block's
+// own shared-memory writes before the signal, without a cluster-wide release
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cta(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cta(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    if (mbar_try_cta(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_cta(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
@@ -225,7 +264,8 @@ __device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
 
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_q,
+decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_kv64,
+                       const __grid_constant__ CUtensorMap map_q,
                        uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
                        float scale_log2, uint32_t* __restrict__ status)
 {
@@ -260,14 +300,14 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         mbar_init(bar(B_KVEMPTY0), N_PV);
         mbar_init(bar(B_KVEMPTY1), N_PV);
         mbar_init(bar(B_SFULL), N_QK);
-        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_THREADS);
-        mbar_init(bar(B_PFULL), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PEMPTY), N_PV);
         mbar_init(bar(B_OFULL), N_PV);
-        mbar_init(bar(B_SYNCA0), PAIR_SOFTMAX_THREADS);
-        mbar_init(bar(B_SYNCA1), PAIR_SOFTMAX_THREADS);
-        mbar_init(bar(B_SYNCB0), PAIR_SOFTMAX_THREADS);
-        mbar_init(bar(B_SYNCB1), PAIR_SOFTMAX_THREADS);
+        mbar_init(bar(B_SYNCA0), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCA1), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCB0), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCB1), PAIR_SOFTMAX_WARPS);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -293,7 +333,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
-                ok = mbar_wait(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
+                ok = mbar_wait_cta(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
                 for (int j = 0; j < NSUB; j++)
@@ -309,7 +349,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
                     if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
-                    ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+                    ok = mbar_wait_cta(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
@@ -326,9 +366,8 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     // V: all 64 tokens, this block's 256 latent dims = sub-tiles 4c+2r, 4c+2r+1 (c = 0, 1)
                     for (int v = 0; v < 4; v++) {
                         const int sub = 4 * (v / 2) + 2 * int(rank) + (v % 2);
-                        for (int hf = 0; hf < 2; hf++)
-                            tma_load_3d_pair(dst + K_BYTES + v * VSUB_BYTES + hf * (VSUB_BYTES / 2), &map_kv,
-                                             leader_kvfull[st], sub * 64, slot0 + 32 * hf, int(layer));
+                        tma_load_3d_pair(dst + K_BYTES + v * VSUB_BYTES, &map_kv64, leader_kvfull[st], sub * 64, slot0,
+                                         int(layer));
                     }
                 }
                 nseg++;
@@ -342,13 +381,17 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             constexpr uint32_t HI = desc_hi(1024);
             const bool is_qk = warp <= N_QK;
             const uint32_t part = is_qk ? warp - 1 : warp - 1 - N_QK;
-            const int c_lo = part == 0 ? 0 : 1 + 2 * int(part), c_hi = 3 + 2 * int(part);
+            const int c_lo = part == 0 ? 0 : 5, c_hi = part == 0 ? 5 : NSUB;            // sub-tiles 0-4 / 5-8
             const uint32_t qk_a = desc_lo(sQ, 16);
             const uint32_t k0 = desc_lo(sST, 16), k1 = desc_lo(sST + STAGE_BYTES, 16);
             const uint32_t v0 = desc_lo(sST + K_BYTES, VSUB_BYTES), v1 = desc_lo(sST + STAGE_BYTES + K_BYTES, VSUB_BYTES);
             const uint32_t pv_b = desc_lo(sP, 16);
             uint32_t t = 0, nseg = 0;
             bool ok = true;
+#ifdef MLA_TC5_TRACE
+            long long tr_wait1 = 0, tr_wait2 = 0, tr_issue = 0;
+            const long long tr0 = clock64();
+#endif
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
@@ -356,8 +399,17 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
                     if (is_qk) {
+#ifdef MLA_TC5_TRACE
+                        const long long a0_ = clock64();
+                        ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status);
+                        const long long a1_ = clock64();
+                        ok = ok && mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+                        const long long a2_ = clock64();
+                        tr_wait1 += a1_ - a0_; tr_wait2 += a2_ - a1_;
+#else
                         ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
                              mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+#endif
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t b0 = st ? k1 : k0;
@@ -377,8 +429,18 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                             if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
                         }
                         __syncwarp();
+#ifdef MLA_TC5_TRACE
+                        tr_issue += clock64() - a2_;
+#endif
                     } else {
+#ifdef MLA_TC5_TRACE
+                        const long long a0_ = clock64();
+#endif
                         ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+#ifdef MLA_TC5_TRACE
+                        const long long a2_ = clock64();
+                        tr_wait1 += a2_ - a0_;
+#endif
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t a0 = (st ? v1 : v0) + ((part * 2 * VSUB_BYTES) >> 4);   // chunk `part`
@@ -393,10 +455,18 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                             if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_OFULL));
                         }
                         __syncwarp();
+#ifdef MLA_TC5_TRACE
+                        tr_issue += clock64() - a2_;
+#endif
                     }
                 }
                 nseg++;
             }
+#ifdef MLA_TC5_TRACE
+            if (blockIdx.x == 6 && blockIdx.y == 0 && lane == 0 && (warp == 1 || warp == 5))
+                printf("[%s issuer] tiles %u total %lld wait_a %lld wait_b %lld issue %lld\n", is_qk ? "qk" : "pv", t,
+                       clock64() - tr0, tr_wait1, tr_wait2, tr_issue);
+#endif
         }
     } else {
         // ===================== softmax / correction / epilogue (both blocks) =====================
@@ -417,7 +487,11 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         float m_used = -INFINITY, l_part = 0.0f;
         uint32_t t = 0, nseg = 0, nb[2] = {0, 0};             // nb: uses of SYNCB[par] so far
         bool fail = false;
-        auto wait_w = [&](uint32_t b, uint32_t parity) {
+        auto wait_w = [&](uint32_t b, uint32_t parity) {              // completion of tensor-core / TMA work
+            if (!fail) fail = !mbar_wait_cta(b, parity, abort_flag, status);
+            fail = __any_sync(0xffffffffu, fail);
+        };
+        auto wait_x = [&](uint32_t b, uint32_t parity) {              // rounds that carry the twin's DSMEM writes
             if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
             fail = __any_sync(0xffffffffu, fail);
         };
@@ -432,6 +506,10 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             return r != 0;
         };
         bool stop = false;
+#ifdef MLA_TC5_TRACE
+        long long ts_wait_s = 0, ts_load = 0, ts_sync = 0, ts_exp = 0, ts_wait_p = 0, ts_store = 0, ts_slow = 0;
+        const long long ts0 = clock64();
+#endif
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
             const SegInfo s = load_seg(m, seg);
             if (s.n_tiles == 0) {
@@ -451,7 +529,14 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             l_part = 0.0f;
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t par = t & 1;
+#ifdef MLA_TC5_TRACE
+                const long long s0_ = clock64();
+#endif
                 wait_w(bar(B_SFULL), t & 1);
+#ifdef MLA_TC5_TRACE
+                const long long s1_ = clock64();
+                ts_wait_s += s1_ - s0_;
+#endif
                 uint32_t sv[32];
                 if (!fail) {
                     tc_fence_after();
@@ -461,17 +546,12 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
-                    tc_ld32(tmem + lane_base + COL_S + 64, sw);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
-                    tc_ld32(tmem + lane_base + COL_S + 96, sw);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
                     tc_fence_before();
-                    if (rank == 0) mbar_arrive_local(bar(B_SEMPTY));
-                    else mbar_arrive_cluster(r_sempty);
+                    __syncwarp();
+                    if (lane == 0) {                       // orders only TMEM reads: no memory release needed
+                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY));
+                        else mbar_arrive_cluster_relaxed(r_sempty);
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i++) sv[i] = 0u;
@@ -487,17 +567,29 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 }
                 // does any head of the pair have to move its reference maximum on this tile?
                 const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
-                if (need && !fail) {
-                    atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
-                    asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
+                // cluster-wide round A: every softmax warp of the pair has posted its flag
+                const bool warp_need = __any_sync(0xffffffffu, need);
+                if (lane == 0 && !fail) {
+                    if (warp_need) {
+                        atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
+                        asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
+                        mbar_arrive_local(bar(B_SYNCA0 + par));
+                        mbar_arrive_cluster(r_synca[par]);
+                    } else {
+                        mbar_arrive_cta(bar(B_SYNCA0 + par));
+                        mbar_arrive_cluster_relaxed(r_synca[par]);
+                    }
                 }
-                // cluster-wide round A: every softmax thread of the pair has posted its flag
-                if (!fail) {
-                    mbar_arrive_local(bar(B_SYNCA0 + par));
-                    mbar_arrive_cluster(r_synca[par]);
-                }
-                wait_w(bar(B_SYNCA0 + par), (t >> 1) & 1);
+#ifdef MLA_TC5_TRACE
+                const long long s2_ = clock64();
+                ts_load += s2_ - s1_;
+#endif
+                wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
                 if (group_or(fail)) { stop = true; break; }
+#ifdef MLA_TC5_TRACE
+                const long long s3_ = clock64();
+                ts_sync += s3_ - s2_;
+#endif
                 const bool slow = need_flag[par] != 0;
                 float alpha = 1.0f;
                 if (slow) {
@@ -513,9 +605,12 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                         asm volatile("st.relaxed.cluster.shared::cluster.f32 [%0], %1;\n"
                                      ::"r"(r_alpha + 4 * (par * 128 + rank * HG + hl)), "f"(alpha) : "memory");
                     }
-                    mbar_arrive_local(bar(B_SYNCB0 + par));
-                    mbar_arrive_cluster(r_syncb[par]);
-                    wait_w(bar(B_SYNCB0 + par), nb[par] & 1);
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive_local(bar(B_SYNCB0 + par));
+                        mbar_arrive_cluster(r_syncb[par]);
+                    }
+                    wait_x(bar(B_SYNCB0 + par), nb[par] & 1);
                     nb[par]++;
                     l_part *= alpha;
                 }
@@ -530,7 +625,16 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 }
                 l_part += sum;
                 // PV of the previous tile must be complete: O is stable and P is free
+#ifdef MLA_TC5_TRACE
+                const long long s4_ = clock64();
+                ts_exp += s4_ - s3_;
+                if (slow) ts_slow++;
+#endif
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
+#ifdef MLA_TC5_TRACE
+                const long long s5_ = clock64();
+                ts_wait_p += s5_ - s4_;
+#endif
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
                 if (slow && j > 0) {
@@ -559,11 +663,17 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 tc_fence_before();
-                if (rank == 0) mbar_arrive_local(bar(B_PFULL));
-                else mbar_arrive_cluster(r_pfull);
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive_cta(bar(B_PFULL));
+                    else mbar_arrive_remote(r_pfull);
+                }
                 // the flag of this parity is next written two tiles from now: clear it once every
                 // thread of the block has read it (they all passed round A of this tile)
                 if (st_id == 0 && slow) need_flag[par] = 0;
+#ifdef MLA_TC5_TRACE
+                ts_store += clock64() - s5_;
+#endif
             }
             if (stop) break;
             // ---- epilogue: O^T (this block's 256 dims x 128 heads) -> acc[head][dim]; (m, l) of own heads
@@ -592,6 +702,11 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             group_or(false);                   // l_other is reused by the next segment
             nseg++;
         }
+#ifdef MLA_TC5_TRACE
+        if ((blockIdx.x == 6 || blockIdx.x == 7) && blockIdx.y == 0 && st_id == 0)
+            printf("[softmax r%u] tiles %u total %lld wait_s %lld load %lld sync %lld exp %lld wait_p %lld store %lld slow %lld\n",
+                   rank, t, clock64() - ts0, ts_wait_s, ts_load, ts_sync, ts_exp, ts_wait_p, ts_store, ts_slow);
+#endif
     }
 
     // Neither block may leave while its twin can still signal its barriers, write its scratch or
@@ -616,7 +731,7 @@ int decode_tc5_pair_configure()
     return int(e);
 }
 
-// tmaps: [1] absorbed queries (box 64 x 64), [2] cache pool with a 64-value x 32-token box.
+// tmaps: [0] cache pool, 64-token box (V); [1] absorbed queries (box 64 x 64); [2] cache pool, 32-token box (K).
 int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
                            float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
 {
@@ -625,10 +740,10 @@ int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
-        decode_tc5_pair_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[1], layer, n_pages, m, recs,
+        decode_tc5_pair_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[0], maps[1], layer, n_pages, m, recs,
                                                                              H, scale_log2, status);
     else
-        decode_tc5_pair_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[1], layer, n_pages, m,
+        decode_tc5_pair_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[0], maps[1], layer, n_pages, m,
                                                                                     recs, H, scale_log2, status);
     return int(cudaGetLastError());
 }
