@@ -60,7 +60,8 @@ struct mla_ctx {
     uint32_t max_segs = 0;
     uint32_t workers = 1;
     uint32_t* status_dev = nullptr;
-    alignas(64) CUtensorMap tmaps[3];   // tcgen05 paths: [0] cache pool (64-token box), [1] absorbed queries, [2] cache pool (32-token box)
+    alignas(64) CUtensorMap tmaps[7];   // + [3..6]: whole-row views (all 9 sub-tiles of a row range in ONE box), see make_tensor_maps
+    // legacy comment follows:   // tcgen05 paths: [0] cache pool (64-token box), [1] absorbed queries, [2] cache pool (32-token box)
 
     // metadata upload ring
     MetaBuf ring[kMetaRing];
@@ -363,6 +364,35 @@ int make_tensor_maps(mla_ctx* c)
                                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS)
             return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool, half page) failed with code " + std::to_string(int(r)));
+    }
+    // Whole-row views: the 576 values of a row are exposed as (64 values, 9 chunks) with the chunk
+    // dimension OUTSIDE the row dimension, so one box {64 values, R rows, C chunks} lands in shared
+    // memory as C consecutive swizzled sub-tiles [R rows][128 B] — a whole operand in ONE TMA
+    // instruction instead of nine (a TMA issue costs its thread ~100 cycles).
+    {
+        const cuuint64_t dims[4] = {64, c->pool_slots, 9, c->cfg.n_layers};
+        const cuuint64_t strides[3] = {cuuint64_t(mla::kRow) * 2, 128, c->pool_slots * mla::kRow * 2};
+        const cuuint32_t estr4[4] = {1, 1, 1, 1};
+        const cuuint32_t boxes[3][4] = {{64, 32, 9, 1}, {64, 64, 2, 1}, {64, 64, 9, 1}};
+        const int slot[3] = {3, 4, 6};
+        for (int i = 0; i < 3; i++) {
+            CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[slot[i]], dt, 4, c->pool, dims, strides, boxes[i], estr4,
+                                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS)
+                return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool, whole-row view " + std::to_string(i) +
+                                                 ") failed with code " + std::to_string(int(r)));
+        }
+        const cuuint64_t qdims[3] = {64, cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64, 9};
+        const cuuint64_t qstrides[2] = {cuuint64_t(mla::kRow) * 2, 128};
+        const cuuint32_t qbox[3] = {64, 64, 9};
+        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[5], dt, 3, c->q_abs, qdims, qstrides, qbox, estr,
+                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(queries, whole-row view) failed with code " + std::to_string(int(r)));
     }
     {   // absorbed queries [max_rows * heads][576]; box = 64 values x 64 head rows
         const cuuint64_t dims[2] = {cuuint64_t(mla::kRow), cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64};

@@ -122,6 +122,16 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, 
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
                  ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -299,13 +309,11 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 ok = mbar_wait(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 mbar_expect_tx(bar(B_QFULL), Q_BYTES);
-                for (int j = 0; j < NSUB; j++)
-                    tma_load_2d(sQ + j * (HG * 128), &map_q, bar(B_QFULL), j * 64, int(s.row * H + h0));
+                tma_load_3d(sQ, &map_q, bar(B_QFULL), 0, int(s.row * H + h0), 0);          // all 9 sub-tiles in one box
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
                 auto prefetch_tile = [&](uint32_t jj) {
                     const uint32_t pg = tbl[s.page_begin + jj];
-                    if (pg < n_pages)
-                        for (int c = 0; c < NSUB; c++) tma_prefetch_3d(&map_kv, c * 64, int(pg * kPage), int(layer));
+                    if (pg < n_pages) tma_prefetch_4d(&map_kv, 0, int(pg * kPage), 0, int(layer));
                 };
                 for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
@@ -326,9 +334,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                     }
                     mbar_expect_tx(bar(B_KVFULL0 + st), KV_STAGE_BYTES);
                     const uint32_t dst = sKV + st * KV_STAGE_BYTES;
-                    for (int c = 0; c < NSUB; c++)
-                        tma_load_3d(dst + c * SUB_BYTES, &map_kv, bar(B_KVFULL0 + st), c * 64, int(page * kPage),
-                                    int(layer));
+                    tma_load_4d(dst, &map_kv, bar(B_KVFULL0 + st), 0, int(page * kPage), 0, int(layer));   // whole page
                 }
                 nseg++;
             }
@@ -660,14 +666,14 @@ int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t 
 {
     (void)q_abs;
     if (m.ctas == 0) return 0;
-    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);   // [0] = cache pool, [1] = Q'
+    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);   // whole-row views: [6] = cache pool, [5] = Q'
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(m.ctas, (H + HG - 1) / HG);
     if (dtype == 0)
-        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], layer, n_pages, m, recs, H,
+        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[6], maps[5], layer, n_pages, m, recs, H,
                                                                         scale_log2, status);
     else
-        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], layer, n_pages, m,
+        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[6], maps[5], layer, n_pages, m,
                                                                                recs, H, scale_log2, status);
     return int(cudaGetLastError());
 }

@@ -177,6 +177,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
         ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
+                                                 int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
                  ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
@@ -330,26 +340,34 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             const uint32_t leader_kvfull[2] = {map_to_rank(bar(B_KVFULL0), 0), map_to_rank(bar(B_KVFULL1), 0)};
             uint32_t t = 0, nseg = 0;
             bool ok = true;
+#ifdef MLA_TC5_TRACE
+            long long tp_wait = 0, tp_issue = 0;
+            const long long tp0 = clock64();
+#endif
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
                 ok = mbar_wait_cta(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
-                for (int j = 0; j < NSUB; j++)
-                    tma_load_2d_pair(sQ + j * (HG * 128), &map_q, leader_qfull, j * 64, int(s.row * H + h0));
+                tma_load_3d_pair(sQ, &map_q, leader_qfull, 0, int(s.row * H + h0), 0);      // all 9 sub-tiles at once
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
                 auto prefetch_tile = [&](uint32_t jj) {
                     const uint32_t pg = tbl[s.page_begin + jj];
-                    if (pg < n_pages)
-                        for (int c = 0; c < NSUB; c++)
-                            tma_prefetch_3d(&map_kv, c * 64, int(pg * kPage + 32 * rank), int(layer));
+                    if (pg < n_pages) tma_prefetch_4d(&map_kv, 0, int(pg * kPage + 32 * rank), 0, int(layer));
                 };
                 for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
                     if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
+#ifdef MLA_TC5_TRACE
+                    const long long p0_ = clock64();
+#endif
                     ok = mbar_wait_cta(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+#ifdef MLA_TC5_TRACE
+                    const long long p1_ = clock64();
+                    tp_wait += p1_ - p0_;
+#endif
                     if (!ok) break;
                     uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
@@ -359,19 +377,22 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     if (rank == 0) mbar_expect_tx(bar(B_KVFULL0 + st), 2 * STAGE_BYTES);
                     const uint32_t dst = sST + st * STAGE_BYTES;
                     const int slot0 = int(page * kPage);
-                    // K: this block's 32 tokens, all 576 dims
-                    for (int c = 0; c < NSUB; c++)
-                        tma_load_3d_pair(dst + c * KSUB_BYTES, &map_kv, leader_kvfull[st], c * 64, slot0 + 32 * int(rank),
-                                         int(layer));
-                    // V: all 64 tokens, this block's 256 latent dims = sub-tiles 4c+2r, 4c+2r+1 (c = 0, 1)
-                    for (int v = 0; v < 4; v++) {
-                        const int sub = 4 * (v / 2) + 2 * int(rank) + (v % 2);
-                        tma_load_3d_pair(dst + K_BYTES + v * VSUB_BYTES, &map_kv64, leader_kvfull[st], sub * 64, slot0,
-                                         int(layer));
-                    }
+                    // K: this block's 32 tokens, all 576 dims, one box
+                    tma_load_4d_pair(dst, &map_kv, leader_kvfull[st], 0, slot0 + 32 * int(rank), 0, int(layer));
+                    // V: all 64 tokens, this block's 256 latent dims = sub-tile pairs (2r, 2r+1) and (4+2r, 4+2r+1)
+                    tma_load_4d_pair(dst + K_BYTES, &map_kv64, leader_kvfull[st], 0, slot0, 2 * int(rank), int(layer));
+                    tma_load_4d_pair(dst + K_BYTES + 2 * VSUB_BYTES, &map_kv64, leader_kvfull[st], 0, slot0, 4 + 2 * int(rank),
+                                     int(layer));
+#ifdef MLA_TC5_TRACE
+                    tp_issue += clock64() - p1_;
+#endif
                 }
                 nseg++;
             }
+#ifdef MLA_TC5_TRACE
+            if (blockIdx.x == 6 && blockIdx.y == 0)
+                printf("[producer] tiles %u total %lld wait_kv_empty %lld issue %lld\n", t, clock64() - tp0, tp_wait, tp_issue);
+#endif
         }
     } else if (warp <= N_QK + N_PV) {
         // ===================== MMA issuers (pair leader only) =====================
@@ -731,7 +752,8 @@ int decode_tc5_pair_configure()
     return int(e);
 }
 
-// tmaps: [0] cache pool, 64-token box (V); [1] absorbed queries (box 64 x 64); [2] cache pool, 32-token box (K).
+// tmaps (whole-row views): [3] pool, box 32 tokens x 9 chunks (K); [4] pool, box 64 tokens x 2 chunks (V);
+// [5] absorbed queries, box 64 rows x 9 chunks.
 int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
                            float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
 {
@@ -740,10 +762,10 @@ int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
-        decode_tc5_pair_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[0], maps[1], layer, n_pages, m, recs,
+        decode_tc5_pair_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[3], maps[4], maps[5], layer, n_pages, m, recs,
                                                                              H, scale_log2, status);
     else
-        decode_tc5_pair_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[2], maps[0], maps[1], layer, n_pages, m,
+        decode_tc5_pair_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[3], maps[4], maps[5], layer, n_pages, m,
                                                                                     recs, H, scale_log2, status);
     return int(cudaGetLastError());
 }
