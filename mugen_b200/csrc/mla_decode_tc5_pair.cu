@@ -67,14 +67,14 @@ constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
 constexpr uint32_t COL_S = 256;     // N_QK partial score tiles x 32 columns
 
 constexpr int N_QK = 2, N_PV = 2;                   // pair MMAs issue quickly: two issuers each suffice
-constexpr int NUM_THREADS = 32 * (1 + N_QK + N_PV + 4);
+constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 4);   // K producer, issuers, V producer, 4 softmax warps
 constexpr int SOFTMAX_THREADS = 128;
 constexpr int PAIR_SOFTMAX_WARPS = 8;               // barriers fed by the softmax role count warps, not threads
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 constexpr int PREFETCH_TILES = 4;
 
-enum { B_QFULL = 0, B_QEMPTY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_SEMPTY, B_PFULL, B_PEMPTY,
+enum { B_QFULL = 0, B_QEMPTY, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_SFULL, B_SEMPTY, B_PFULL, B_PEMPTY,
        B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -305,10 +305,14 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         need_flag[0] = need_flag[1] = 0;
         mbar_init(bar(B_QFULL), 1);
         mbar_init(bar(B_QEMPTY), N_QK);
-        mbar_init(bar(B_KVFULL0), 1);
-        mbar_init(bar(B_KVFULL1), 1);
-        mbar_init(bar(B_KVEMPTY0), N_PV);
-        mbar_init(bar(B_KVEMPTY1), N_PV);
+        mbar_init(bar(B_KFULL0), 1);
+        mbar_init(bar(B_KFULL1), 1);
+        mbar_init(bar(B_KEMPTY0), N_QK);
+        mbar_init(bar(B_KEMPTY1), N_QK);
+        mbar_init(bar(B_VFULL0), 1);
+        mbar_init(bar(B_VFULL1), 1);
+        mbar_init(bar(B_VEMPTY0), N_PV);
+        mbar_init(bar(B_VEMPTY1), N_PV);
         mbar_init(bar(B_SFULL), N_QK);
         mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
@@ -334,65 +338,76 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
     if (warp == 0) {
-        // ===================== TMA producer (each block fetches its own boxes) =====================
+        // ===================== TMA producer for Q' and K (each block fetches its own boxes) =====================
+        // K and V of a tile live in separate stages with separate barriers: the K half is free again
+        // as soon as the scores are computed, long before PV releases the V half, so the next K load
+        // overlaps the softmax instead of waiting for it.
         if (lane == 0) {
             const uint32_t leader_qfull = map_to_rank(bar(B_QFULL), 0);
-            const uint32_t leader_kvfull[2] = {map_to_rank(bar(B_KVFULL0), 0), map_to_rank(bar(B_KVFULL1), 0)};
+            const uint32_t leader_kfull[2] = {map_to_rank(bar(B_KFULL0), 0), map_to_rank(bar(B_KFULL1), 0)};
             uint32_t t = 0, nseg = 0;
             bool ok = true;
-#ifdef MLA_TC5_TRACE
-            long long tp_wait = 0, tp_issue = 0;
-            const long long tp0 = clock64();
-#endif
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
                 ok = mbar_wait_cta(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
                 tma_load_3d_pair(sQ, &map_q, leader_qfull, 0, int(s.row * H + h0), 0);      // all 9 sub-tiles at once
-                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
-                auto prefetch_tile = [&](uint32_t jj) {
-                    const uint32_t pg = tbl[s.page_begin + jj];
-                    if (pg < n_pages) tma_prefetch_4d(&map_kv, 0, int(pg * kPage + 32 * rank), 0, int(layer));
-                };
-                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
+                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) {
+                    const uint32_t pg = tbl[jj];
+                    if (pg < n_pages) tma_prefetch_4d(&map_kv64, 0, int(pg * kPage), 4 * int(rank), int(layer));
+                }
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
-                    if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
-#ifdef MLA_TC5_TRACE
-                    const long long p0_ = clock64();
-#endif
-                    ok = mbar_wait_cta(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
-#ifdef MLA_TC5_TRACE
-                    const long long p1_ = clock64();
-                    tp_wait += p1_ - p0_;
-#endif
+                    // page ids first: their latency hides behind the wait
+                    uint32_t page = tbl[j];
+                    const uint32_t pf = (j + PREFETCH_TILES < s.n_tiles) ? tbl[j + PREFETCH_TILES] : 0xffffffffu;
+                    ok = mbar_wait_cta(bar(B_KEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
-                    uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
                         atomicOr(status, ST_BAD_PAGE);
                         page = 0;
                     }
-                    if (rank == 0) mbar_expect_tx(bar(B_KVFULL0 + st), 2 * STAGE_BYTES);
-                    const uint32_t dst = sST + st * STAGE_BYTES;
-                    const int slot0 = int(page * kPage);
-                    // K: this block's 32 tokens, all 576 dims, one box
-                    tma_load_4d_pair(dst, &map_kv, leader_kvfull[st], 0, slot0 + 32 * int(rank), 0, int(layer));
-                    // V: all 64 tokens, this block's 256 latent dims = sub-tile pairs (2r, 2r+1) and (4+2r, 4+2r+1)
-                    tma_load_4d_pair(dst + K_BYTES, &map_kv64, leader_kvfull[st], 0, slot0, 2 * int(rank), int(layer));
-                    tma_load_4d_pair(dst + K_BYTES + 2 * VSUB_BYTES, &map_kv64, leader_kvfull[st], 0, slot0, 4 + 2 * int(rank),
+                    if (rank == 0) mbar_expect_tx(bar(B_KFULL0 + st), 2 * K_BYTES);
+                    tma_load_4d_pair(sST + st * STAGE_BYTES, &map_kv, leader_kfull[st], 0, int(page * kPage) + 32 * int(rank), 0,
                                      int(layer));
-#ifdef MLA_TC5_TRACE
-                    tp_issue += clock64() - p1_;
-#endif
+                    // L2 prefetch of a later page: block r pulls sub-tiles 4r .. 4r+4 (the pair covers all 9 with the
+                    // second call below), so the real loads of both blocks hit L2
+                    if (pf < n_pages) {
+                        tma_prefetch_4d(&map_kv64, 0, int(pf * kPage), 4 * int(rank), int(layer));
+                        tma_prefetch_4d(&map_kv64, 0, int(pf * kPage), 4 * int(rank) + 2, int(layer));
+                        if (rank == 1) tma_prefetch_4d(&map_kv64, 0, int(pf * kPage), 7, int(layer));
+                    }
                 }
                 nseg++;
             }
-#ifdef MLA_TC5_TRACE
-            if (blockIdx.x == 6 && blockIdx.y == 0)
-                printf("[producer] tiles %u total %lld wait_kv_empty %lld issue %lld\n", t, clock64() - tp0, tp_wait, tp_issue);
-#endif
+        }
+    } else if (warp == N_QK + N_PV + 1) {
+        // ===================== TMA producer for V =====================
+        if (lane == 0) {
+            const uint32_t leader_vfull[2] = {map_to_rank(bar(B_VFULL0), 0), map_to_rank(bar(B_VFULL1), 0)};
+            uint32_t t = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
+                for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                    const uint32_t st = t % KV_STAGES;
+                    uint32_t page = tbl[j];
+                    ok = mbar_wait_cta(bar(B_VEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
+                    if (!ok) break;
+                    if (page >= n_pages) page = 0;           // flagged by the K producer
+                    if (rank == 0) mbar_expect_tx(bar(B_VFULL0 + st), 2 * V_BYTES);
+                    const uint32_t dst = sST + st * STAGE_BYTES + K_BYTES;
+                    const int slot0 = int(page * kPage);
+                    // all 64 tokens, this block's 256 latent dims = sub-tile pairs (2r, 2r+1) and (4+2r, 4+2r+1)
+                    tma_load_4d_pair(dst, &map_kv64, leader_vfull[st], 0, slot0, 2 * int(rank), int(layer));
+                    tma_load_4d_pair(dst + 2 * VSUB_BYTES, &map_kv64, leader_vfull[st], 0, slot0, 4 + 2 * int(rank), int(layer));
+                }
+            }
         }
     } else if (warp <= N_QK + N_PV) {
         // ===================== MMA issuers (pair leader only) =====================
@@ -422,13 +437,13 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     if (is_qk) {
 #ifdef MLA_TC5_TRACE
                         const long long a0_ = clock64();
-                        ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status);
+                        ok = mbar_wait(bar(B_KFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status);
                         const long long a1_ = clock64();
                         ok = ok && mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
                         const long long a2_ = clock64();
                         tr_wait1 += a1_ - a0_; tr_wait2 += a2_ - a1_;
 #else
-                        ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
+                        ok = mbar_wait(bar(B_KFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
                              mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
 #endif
                         if (!ok) break;
@@ -447,6 +462,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                                 }
                             }
                             tc_commit_pair(bar(B_SFULL));
+                            tc_commit_pair(bar(B_KEMPTY0 + st));
                             if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
                         }
                         __syncwarp();
@@ -457,7 +473,8 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
 #ifdef MLA_TC5_TRACE
                         const long long a0_ = clock64();
 #endif
-                        ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+                        ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status) &&
+                             mbar_wait(bar(B_VFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status);
 #ifdef MLA_TC5_TRACE
                         const long long a2_ = clock64();
                         tr_wait1 += a2_ - a0_;
@@ -471,7 +488,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                             for (int k = 0; k < TILE / 16; k++)
                                 tc_mma_pair(tmem + COL_O + part * (2 * HG), a0 + ((k * 2048) >> 4), HI, pv_b + ((k * 32) >> 4),
                                             HI, IDESC_PV, k == 0 ? fresh : 1u);
-                            tc_commit_pair(bar(B_KVEMPTY0 + st));
+                            tc_commit_pair(bar(B_VEMPTY0 + st));
                             tc_commit_pair(bar(B_PEMPTY));
                             if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_OFULL));
                         }
@@ -484,7 +501,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 nseg++;
             }
 #ifdef MLA_TC5_TRACE
-            if (blockIdx.x == 6 && blockIdx.y == 0 && lane == 0 && (warp == 1 || warp == 5))
+            if (blockIdx.x == 6 && blockIdx.y == 0 && lane == 0 && (warp == 1 || warp == N_QK + 1))
                 printf("[%s issuer] tiles %u total %lld wait_a %lld wait_b %lld issue %lld\n", is_qk ? "qk" : "pv", t,
                        clock64() - tr0, tr_wait1, tr_wait2, tr_issue);
 #endif
