@@ -35,6 +35,7 @@ METRIC, UNIT = "mla_decode_tokens_per_s", "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at the default workload
 # (profiles/decode_tc5_kernel_v3shape_b64_ctx16384.md); only meaningful for that workload and kernel
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.292e9
+NCU_TRAFFIC_KERNEL = "tcgen05"
 
 
 def parse_args():
@@ -284,7 +285,7 @@ def run_ours(a):
     per_launch_s = (attn_ms * 1e-3) / max(1, n_attn)
     achieved = algo_bytes / per_launch_s / 1e9 if per_launch_s > 0 else 0.0
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * (B / 64.0) if (ctx.kernel_name() == "tcgen05" and a.heads == 128 and a.ctx == 16384) else None, "kernel": f"split-KV attention ({ctx.kernel_name()})",
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * (B / 64.0) if (ctx.kernel_name() == NCU_TRAFFIC_KERNEL and a.heads == 128 and a.ctx == 16384) else None, "kernel": f"split-KV attention ({ctx.kernel_name()})",
                 "peak_source": peak_src, "algorithmic_bytes_per_launch": algo_bytes,
                 "avg_launch_us": per_launch_s * 1e6, "launches_timed": n_attn}
     # whole layer-step view of the same thing (all kernels of the step, cache term only)

@@ -456,8 +456,11 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (prop.major != 10)
         { cp->err = "this library is built for sm_100a only; device is sm_" + std::to_string(prop.major * 10 + prop.minor);
           return bail(MLA_ERR_UNSUPPORTED); }
-    // wide head counts fill the 64-row tcgen05 tiles; narrow ones map 1:1 onto m16n8k16
-    c->kernel = cfg->kernel == MLA_KERNEL_AUTO ? (cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA) : cfg->kernel;
+    // 128-head groups go to the SM-pair kernel, other wide head counts fill the 64-row tcgen05
+    // tiles of the single-block kernel, narrow ones map 1:1 onto m16n8k16
+    c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
+              : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR
+              : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA;
     const uint32_t H = cfg->n_heads;
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));

@@ -50,7 +50,7 @@ constexpr int OFF_Q = 0;
 constexpr int OFF_ST = OFF_Q + Q_BYTES;
 constexpr int OFF_P = OFF_ST + KV_STAGES * STAGE_BYTES;
 constexpr int OFF_MISC = OFF_P + P_BYTES;
-constexpr int MISC_BYTES = 3072;
+constexpr int MISC_BYTES = 3584;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 
 // misc area layout (bytes from OFF_MISC)
@@ -59,17 +59,17 @@ constexpr int M_TMEM = 256;       // tmem base
 constexpr int M_ABORT = 260;
 constexpr int M_FLAG = 264;       // [2] "some head of the pair must move its maximum", by tile parity
 constexpr int M_ALPHA = 512;      // [2][128] floats: scale factor per head of the pair, by tile parity
-constexpr int M_HMAX = 1536;      // [2][64] floats: tile maximum of each token half per head
-constexpr int M_LSUM = 2048;      // [64] floats: second half's partial sum at the epilogue
+constexpr int M_HMAX = 1536;      // [4][64] floats: tile maximum of each token quarter per head
+constexpr int M_LSUM = 2560;      // [3][64] floats: the other quarters' partial sums at the epilogue
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
 constexpr uint32_t COL_S = 256;     // N_QK partial score tiles x 32 columns
 
 constexpr int N_QK = 2, N_PV = 2;                   // pair MMAs issue quickly: two issuers each suffice
-constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 4);   // K producer, issuers, V producer, 4 softmax warps
-constexpr int SOFTMAX_THREADS = 128;
-constexpr int PAIR_SOFTMAX_WARPS = 8;               // barriers fed by the softmax role count warps, not threads
+constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 8);   // K producer, issuers, V producer, 8 softmax warps
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int PAIR_SOFTMAX_WARPS = 16;              // barriers fed by the softmax role count warps, not threads
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 constexpr int PREFETCH_TILES = 4;
@@ -224,6 +224,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -507,16 +515,19 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
 #endif
         }
     } else {
-        // ===================== softmax / correction / epilogue (both blocks) =====================
-        // S of a pair MMA with 64 rows per block: head row r sits in TMEM lane r (tokens 0-31 of
-        // the tile) and lane 64+r (tokens 32-63).  Thread = one lane: (head, token half).
+        // ===================== softmax / correction / epilogue (both blocks, 8 warps) =====================
+        // S of a pair MMA with 64 rows per block: head row r sits in TMEM lane r (tokens 0-31 of the
+        // tile) and lane 64+r (tokens 32-63).  Two warps share each lane quarter and split its 32
+        // columns, so a thread owns (head, 16 tokens): token quarter tq = 2*half + group.
+        const uint32_t sw_id = warp - (2 + N_QK + N_PV);      // 0..7
+        const uint32_t grp = sw_id / 4;                       // column group within the lane quarter
         const uint32_t q4 = warp % 4;
         const uint32_t lane_base = (q4 * 32u) << 16;
-        const uint32_t half = q4 / 2;                         // which 32 tokens of the tile
+        const uint32_t half = q4 / 2;
+        const uint32_t tq = 2 * half + grp;                   // tokens 16*tq .. 16*tq+15 of the tile
         const uint32_t hl = 32 * (q4 % 2) + lane;             // head within this block's 64
         const uint32_t st_id = tid - (NUM_THREADS - SOFTMAX_THREADS);
         const uint32_t peer = rank ^ 1;
-        // remote twins of the barriers and scratch words this thread signals
         const uint32_t r_sempty = map_to_rank(bar(B_SEMPTY), 0), r_pfull = map_to_rank(bar(B_PFULL), 0);
         const uint32_t r_synca[2] = {map_to_rank(bar(B_SYNCA0), peer), map_to_rank(bar(B_SYNCA1), peer)};
         const uint32_t r_syncb[2] = {map_to_rank(bar(B_SYNCB0), peer), map_to_rank(bar(B_SYNCB1), peer)};
@@ -533,21 +544,17 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
             fail = __any_sync(0xffffffffu, fail);
         };
-        auto group_or = [&](bool pred) -> bool {              // barrier over this block's 128 threads + OR
+        auto group_or = [&](bool pred) -> bool {              // barrier over this block's softmax threads + OR
             uint32_t r;
             asm volatile(
                 "{\n.reg .pred pi, po;\n"
                 "setp.ne.b32 pi, %1, 0;\n"
-                "barrier.cta.red.or.pred po, 1, 128, pi;\n"
+                "barrier.cta.red.or.pred po, 1, 256, pi;\n"
                 "selp.u32 %0, 1, 0, po;\n}\n"
                 : "=r"(r) : "r"(uint32_t(pred)) : "memory");
             return r != 0;
         };
         bool stop = false;
-#ifdef MLA_TC5_TRACE
-        long long ts_wait_s = 0, ts_load = 0, ts_sync = 0, ts_exp = 0, ts_wait_p = 0, ts_store = 0, ts_slow = 0;
-        const long long ts0 = clock64();
-#endif
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
             const SegInfo s = load_seg(m, seg);
             if (s.n_tiles == 0) {
@@ -555,10 +562,8 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                 for (uint32_t h = 0; h < 2 * HG; h++) {
                     if (hpair + h >= H) break;
                     float* rc = recs + (size_t(seg) * H + hpair + h) * kPart;
-                    for (uint32_t d = st_id; d < 256; d += SOFTMAX_THREADS) {
-                        const uint32_t dim = (d / 128) * 256 + rank * 128 + (d % 128);
-                        rc[2 + dim] = 0.0f;
-                    }
+                    const uint32_t dim = (st_id / 128) * 256 + rank * 128 + (st_id % 128);
+                    rc[2 + dim] = 0.0f;
                     if (st_id == 0 && h / HG == rank) { rc[0] = -INFINITY; rc[1] = 0.0f; }
                 }
                 continue;
@@ -567,23 +572,16 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             l_part = 0.0f;
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t par = t & 1;
-#ifdef MLA_TC5_TRACE
-                const long long s0_ = clock64();
-#endif
                 wait_w(bar(B_SFULL), t & 1);
-#ifdef MLA_TC5_TRACE
-                const long long s1_ = clock64();
-                ts_wait_s += s1_ - s0_;
-#endif
-                uint32_t sv[32];
+                uint32_t sv[16];
                 if (!fail) {
                     tc_fence_after();
-                    uint32_t sw[32];
-                    tc_ld32(tmem + lane_base + COL_S, sv);
-                    tc_ld32(tmem + lane_base + COL_S + 32, sw);
+                    uint32_t sw[16];
+                    tc_ld16(tmem + lane_base + COL_S + grp * 16, sv);
+                    tc_ld16(tmem + lane_base + COL_S + 32 + grp * 16, sw);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    for (int i = 0; i < 16; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {                       // orders only TMEM reads: no memory release needed
@@ -592,20 +590,19 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) sv[i] = 0u;
+                    for (int i = 0; i < 16; i++) sv[i] = 0u;
                 }
                 const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
                 float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
+                for (int i = 0; i < 16; i++) {
                     float v = __uint_as_float(sv[i]) * scale_log2;
-                    v = (half * 32 + uint32_t(i) < valid) ? v : -INFINITY;
+                    v = (tq * 16 + uint32_t(i) < valid) ? v : -INFINITY;
                     sv[i] = __float_as_uint(v);
                     mx = fmaxf(mx, v);
                 }
                 // does any head of the pair have to move its reference maximum on this tile?
                 const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
-                // cluster-wide round A: every softmax warp of the pair has posted its flag
                 const bool warp_need = __any_sync(0xffffffffu, need);
                 if (lane == 0 && !fail) {
                     if (warp_need) {
@@ -618,27 +615,30 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                         mbar_arrive_cluster_relaxed(r_synca[par]);
                     }
                 }
-#ifdef MLA_TC5_TRACE
-                const long long s2_ = clock64();
-                ts_load += s2_ - s1_;
-#endif
+                // optimistic: exponentials against the current maximum while the cluster round is in
+                // flight; they stand unless some head of the pair raised the flag
+                float sum = 0.0f;
+                uint32_t pk[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
+                    const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                    sum += p0 + p1;
+                    pk[i / 2] = Elem<T>::pack2(p0, p1);
+                }
                 wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
                 if (group_or(fail)) { stop = true; break; }
-#ifdef MLA_TC5_TRACE
-                const long long s3_ = clock64();
-                ts_sync += s3_ - s2_;
-#endif
                 const bool slow = need_flag[par] != 0;
-                float alpha = 1.0f;
                 if (slow) {
-                    // exchange the two halves' maxima inside the block, decide per head, publish the
-                    // scale factors to both blocks
-                    half_max[half * HG + hl] = mx;
+                    // exchange the token quarters' maxima inside the block, decide per head, publish the
+                    // scale factors to both blocks, and redo the exponentials
+                    float alpha = 1.0f;
+                    half_max[tq * HG + hl] = mx;
                     group_or(false);
-                    const float mrow = fmaxf(half_max[hl], half_max[HG + hl]);
+                    const float mrow = fmaxf(fmaxf(half_max[hl], half_max[HG + hl]), fmaxf(half_max[2 * HG + hl], half_max[3 * HG + hl]));
                     if (j == 0) { m_used = mrow; alpha = 0.0f; }
                     else if (mrow > m_used + RESCALE_THRESHOLD) { alpha = fast_ex2(m_used - mrow); m_used = mrow; }
-                    if (half == 0) {
+                    if (tq == 0) {
                         alpha_all[par * 128 + rank * HG + hl] = alpha;
                         asm volatile("st.relaxed.cluster.shared::cluster.f32 [%0], %1;\n"
                                      ::"r"(r_alpha + 4 * (par * 128 + rank * HG + hl)), "f"(alpha) : "memory");
@@ -651,39 +651,29 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     wait_x(bar(B_SYNCB0 + par), nb[par] & 1);
                     nb[par]++;
                     l_part *= alpha;
-                }
-                float sum = 0.0f;
-                uint32_t pk[16];
+                    sum = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
-                    const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
-                    sum += p0 + p1;
-                    pk[i / 2] = Elem<T>::pack2(p0, p1);
+                    for (int i = 0; i < 16; i += 2) {
+                        const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
+                        const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                        sum += p0 + p1;
+                        pk[i / 2] = Elem<T>::pack2(p0, p1);
+                    }
                 }
                 l_part += sum;
                 // PV of the previous tile must be complete: O is stable and P is free
-#ifdef MLA_TC5_TRACE
-                const long long s4_ = clock64();
-                ts_exp += s4_ - s3_;
-                if (slow) ts_slow++;
-#endif
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
-#ifdef MLA_TC5_TRACE
-                const long long s5_ = clock64();
-                ts_wait_p += s5_ - s4_;
-#endif
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
                 if (slow && j > 0) {
-                    // O^T[this block's dims][128 heads] *= alpha[head], both chunks
+                    // O^T[this block's dims][128 heads] *= alpha[head]; each warp group takes one chunk
 #pragma unroll 1
-                    for (int c = 0; c < 8; c++) {
+                    for (int c = 0; c < 4; c++) {
                         uint32_t o[32];
-                        const uint32_t col = COL_O + c * 32;
+                        const uint32_t col = COL_O + grp * 128 + c * 32;
                         tc_ld32(tmem + lane_base + col, o);
                         tc_wait_ld();
-                        const float* al = alpha_all + par * 128 + (c & 3) * 32;
+                        const float* al = alpha_all + par * 128 + c * 32;
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * al[i]);
                         tc_st32(tmem + lane_base + col, o);
@@ -691,12 +681,12 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     tc_wait_st();
                 }
                 {
-                    // row hl of the K-major swizzled P tile, this thread's 32 tokens = chunks 4*half .. +3
+                    // row hl of the K-major swizzled P tile, this thread's 16 tokens = chunks 2*tq, 2*tq+1
                     unsigned char* prow = sm + OFF_P + hl * 128;
 #pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {
+                    for (int ch = 0; ch < 2; ch++) {
                         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-                        *reinterpret_cast<uint4*>(prow + (((4 * half + ch) ^ (hl & 7)) << 4)) = v;
+                        *reinterpret_cast<uint4*>(prow + (((2 * tq + ch) ^ (hl & 7)) << 4)) = v;
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -707,44 +697,36 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                     else mbar_arrive_remote(r_pfull);
                 }
                 // the flag of this parity is next written two tiles from now: clear it once every
-                // thread of the block has read it (they all passed round A of this tile)
+                // thread of the block has read it (they all passed the barrier of the slow path)
                 if (st_id == 0 && slow) need_flag[par] = 0;
-#ifdef MLA_TC5_TRACE
-                ts_store += clock64() - s5_;
-#endif
             }
             if (stop) break;
             // ---- epilogue: O^T (this block's 256 dims x 128 heads) -> acc[head][dim]; (m, l) of own heads
             wait_w(bar(B_OFULL), nseg & 1);
-            if (half == 1) l_other[hl] = l_part;
+            if (tq != 0) l_other[(tq - 1) * HG + hl] = l_part;
             if (group_or(fail)) { stop = true; break; }
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < 4; c++) {                      // warp group `grp` owns chunk `grp`
                 uint32_t o[32];
-                tc_ld32(tmem + lane_base + COL_O + c * 32, o);
+                tc_ld32(tmem + lane_base + COL_O + grp * 128 + c * 32, o);
                 tc_wait_ld();
-                const uint32_t dim = (c / 4) * 256 + rank * 128 + q4 * 32 + lane;
-                const uint32_t hb = hpair + (c & 3) * 32;
+                const uint32_t dim = grp * 256 + rank * 128 + q4 * 32 + lane;
+                const uint32_t hb = hpair + c * 32;
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     if (hb + i < H) recs[(size_t(seg) * H + hb + i) * kPart + 2 + dim] = __uint_as_float(o[i]);
                 }
             }
-            if (half == 0 && h0 + hl < H) {
+            if (tq == 0 && h0 + hl < H) {
                 float* rc = recs + (size_t(seg) * H + h0 + hl) * kPart;
                 rc[0] = m_used;
-                rc[1] = l_part + l_other[hl];
+                rc[1] = l_part + l_other[hl] + l_other[HG + hl] + l_other[2 * HG + hl];
             }
             tc_fence_before();
             group_or(false);                   // l_other is reused by the next segment
             nseg++;
         }
-#ifdef MLA_TC5_TRACE
-        if ((blockIdx.x == 6 || blockIdx.x == 7) && blockIdx.y == 0 && st_id == 0)
-            printf("[softmax r%u] tiles %u total %lld wait_s %lld load %lld sync %lld exp %lld wait_p %lld store %lld slow %lld\n",
-                   rank, t, clock64() - ts0, ts_wait_s, ts_load, ts_sync, ts_exp, ts_wait_p, ts_store, ts_slow);
-#endif
     }
 
     // Neither block may leave while its twin can still signal its barriers, write its scratch or

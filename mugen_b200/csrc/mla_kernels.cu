@@ -140,32 +140,27 @@ __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uin
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Block = (head, 16 query rows, quarter of the 512 output columns); C[16 x 128] = q_nope[16 x 128] .
-// W_UK_h[128 x 128 cols] on the warp-level tensor path (m16n8k16, f32 accumulate).  The weight is
-// read from its transposed copy W_UK^T[h][d][i] (made once at registration) so that B fragments are
-// plain 4-byte loads with the contraction index contiguous.  Each warp owns 32 output columns and
-// issues all of its 64 weight loads before the first MMA: one L2 round trip per block, and enough
-// blocks (H x row tiles x 4) to fill the GPU at small batch.
+// Block = (head, quarter of the 512 output columns, group of up to 8 row tiles of 16 query rows);
+// C[16 x 128] = q_nope[16 x 128] . W_UK_h[128 x 128 cols] per row tile on the warp-level tensor path
+// (m16n8k16, f32 accumulate).  The weight is read from its transposed copy W_UK^T[h][d][i] (made
+// once at registration), so B fragments are 16-byte loads with the contraction index contiguous;
+// a warp loads the fragments of its 32 output columns ONCE and reuses them for every row tile of
+// the block, so W_UK crosses L2 once per 128 query rows.
+// 16-byte operand loads: within each block of 32 contraction indices, thread t4 takes indices
+// 8*t4 .. 8*t4+7 of its row, for A and for B alike.  The pairs (0,1),(2,3) feed one MMA as
+// (k, k+8) and (4,5),(6,7) the next: a fixed permutation of the contraction index applied to both
+// operands, which leaves the product unchanged.
+constexpr int kAbsorbTilesPerBlock = 8;
 template <typename T>
 __global__ void __launch_bounds__(128)
 absorb_kernel(const T* __restrict__ q, const T* __restrict__ w_uk_t, T* __restrict__ q_abs,
               uint32_t rows, uint32_t H)
 {
-    const uint32_t h = blockIdx.x, r0 = blockIdx.y * 16, nq = blockIdx.z, tid = threadIdx.x;
+    const uint32_t h = blockIdx.x, nq = blockIdx.z, tid = threadIdx.x;
     const uint32_t warp = tid / 32, lane = tid % 32, g = lane / 4, t4 = lane % 4;
-    if (nq == 0) {
-        for (int idx = tid; idx < 16 * (kRope / 2); idx += 128) {        // rope part: straight copy
-            const uint32_t rr = idx / (kRope / 2), k = idx % (kRope / 2), r = r0 + rr;
-            if (r < rows)
-                reinterpret_cast<uint32_t*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[k] =
-                    reinterpret_cast<const uint32_t*>(q + (size_t(r) * H + h) * kQDim + kNope)[k];
-        }
-    }
+    const uint32_t rt_begin = blockIdx.y * kAbsorbTilesPerBlock;
+    const uint32_t rt_end = min(rt_begin + kAbsorbTilesPerBlock, (rows + 15) / 16);
     const int col0 = nq * 128 + warp * 32;                     // this warp's 32 output columns
-    // 16-byte loads: within each block of 32 contraction indices, thread t4 takes indices
-    // 8*t4 .. 8*t4+7 of its row, for A and for B alike.  The pairs (0,1),(2,3) feed one MMA as
-    // (k, k+8) and (4,5),(6,7) the next: a fixed permutation of the contraction index applied to
-    // both operands, which leaves the product unchanged.
     uint4 b[4][kNope / 32];
 #pragma unroll
     for (int nt = 0; nt < 4; nt++) {
@@ -173,8 +168,17 @@ absorb_kernel(const T* __restrict__ q, const T* __restrict__ w_uk_t, T* __restri
 #pragma unroll
         for (int kb = 0; kb < kNope / 32; kb++) b[nt][kb] = *reinterpret_cast<const uint4*>(wrow + kb * 32);
     }
-    uint4 a0[kNope / 32], a1[kNope / 32];
-    {
+    for (uint32_t rt = rt_begin; rt < rt_end; rt++) {
+        const uint32_t r0 = rt * 16;
+        if (nq == 0) {
+            for (int idx = tid; idx < 16 * (kRope / 2); idx += 128) {        // rope part: straight copy
+                const uint32_t rr = idx / (kRope / 2), k = idx % (kRope / 2), r = r0 + rr;
+                if (r < rows)
+                    reinterpret_cast<uint32_t*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[k] =
+                        reinterpret_cast<const uint32_t*>(q + (size_t(r) * H + h) * kQDim + kNope)[k];
+            }
+        }
+        uint4 a0[kNope / 32], a1[kNope / 32];
         const bool v0 = r0 + g < rows, v1 = r0 + g + 8 < rows;
         const T* q0 = q + (size_t(r0 + g) * H + h) * kQDim + t4 * 8;
         const T* q1 = q + (size_t(r0 + g + 8) * H + h) * kQDim + t4 * 8;
@@ -183,22 +187,20 @@ absorb_kernel(const T* __restrict__ q, const T* __restrict__ w_uk_t, T* __restri
             a0[kb] = v0 ? *reinterpret_cast<const uint4*>(q0 + kb * 32) : make_uint4(0, 0, 0, 0);
             a1[kb] = v1 ? *reinterpret_cast<const uint4*>(q1 + kb * 32) : make_uint4(0, 0, 0, 0);
         }
-    }
 #pragma unroll
-    for (int nt = 0; nt < 4; nt++) {
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int nt = 0; nt < 4; nt++) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int kb = 0; kb < kNope / 32; kb++) {
-            const uint32_t f0[4] = {a0[kb].x, a1[kb].x, a0[kb].y, a1[kb].y};
-            const uint32_t f1[4] = {a0[kb].z, a1[kb].z, a0[kb].w, a1[kb].w};
-            mma16816<T>(c, f0, b[nt][kb].x, b[nt][kb].y);
-            mma16816<T>(c, f1, b[nt][kb].z, b[nt][kb].w);
+            for (int kb = 0; kb < kNope / 32; kb++) {
+                const uint32_t f0[4] = {a0[kb].x, a1[kb].x, a0[kb].y, a1[kb].y};
+                const uint32_t f1[4] = {a0[kb].z, a1[kb].z, a0[kb].w, a1[kb].w};
+                mma16816<T>(c, f0, b[nt][kb].x, b[nt][kb].y);
+                mma16816<T>(c, f1, b[nt][kb].z, b[nt][kb].w);
+            }
+            const int col = col0 + nt * 8 + t4 * 2;
+            if (v0) *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g) * H + h) * kRow + col) = Elem<T>::pack2(c[0], c[1]);
+            if (v1) *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g + 8) * H + h) * kRow + col) = Elem<T>::pack2(c[2], c[3]);
         }
-        const int col = col0 + nt * 8 + t4 * 2;
-        if (r0 + g < rows)
-            *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g) * H + h) * kRow + col) = Elem<T>::pack2(c[0], c[1]);
-        if (r0 + g + 8 < rows)
-            *reinterpret_cast<uint32_t*>(q_abs + (size_t(r0 + g + 8) * H + h) * kRow + col) = Elem<T>::pack2(c[2], c[3]);
     }
 }
 
@@ -206,7 +208,8 @@ void launch_absorb(int dtype, const void* q, const void* w_uk_t, void* q_abs, ui
                    uint32_t H, cudaStream_t st)
 {
     if (rows == 0) return;
-    dim3 grid(H, (rows + 15) / 16, 4);
+    const uint32_t row_tiles = (rows + 15) / 16;
+    dim3 grid(H, (row_tiles + kAbsorbTilesPerBlock - 1) / kAbsorbTilesPerBlock, 4);
     if (dtype == 0)
         absorb_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(q), static_cast<const __half*>(w_uk_t),
                                                     static_cast<__half*>(q_abs), rows, H);
@@ -305,109 +308,138 @@ merge_outproj_kernel(const float* __restrict__ recs, const uint32_t* __restrict_
     }
 }
 
-// Same merge, projection on the warp-level tensor path.  Block = (head, 16 query rows), 16 warps:
+// Same merge, projection on the warp-level tensor path.  Block = (head, group of up to 4 row tiles
+// of 16 query rows), 16 warps.  W_UV_h (128 x 512, 128 KB) is staged ONCE per block in shared
+// memory with 16-byte loads and serves every row tile of the block.  Per row tile:
 //   1. warp r finds row r's M and 1/L: its lanes take the row's parts in parallel;
 //   2. the merged, normalised o_c[16 x 512] is built in shared memory as TWO 16-bit matrices,
 //      hi = T(o) and lo = T(o - hi): together they carry ~16 (bf16) / 22 (fp16) mantissa bits, so
 //      the float state is not rounded to the storage type before W_UV; thread -> (row, 16 dims);
 //   3. out[16 x 128] = (hi + lo)[16 x 512] . W_UV_h^T, m16n8k16 with f32 accumulate; warp w owns
-//      outputs [8w, 8w+8); W_UV rows are K-contiguous, so B fragments are plain 4-byte loads.
-// Every phase is one or two memory round trips deep, so the kernel stays short at small batch.
+//      outputs [8w, 8w+8), all fragments come from shared memory through ldmatrix.
+constexpr int kMergeTilesPerBlock = 4;
+constexpr int kMergePitch = kRank + 8;               // elements; keeps ldmatrix rows on distinct banks
+constexpr size_t kMergeSmem = size_t(kVDim + 32) * kMergePitch * 2 + 16 * 4 * 4;
 template <typename T>
 __global__ void __launch_bounds__(512)
 merge_outproj_mma_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin,
                          uint32_t n_parts, const T* __restrict__ w_uv, T* __restrict__ out, uint32_t rows,
                          uint32_t H)
 {
-    constexpr int PITCH = kRank + 8;                 // elements; keeps ldmatrix rows on distinct banks
-    __shared__ __align__(16) T a_hi[16 * PITCH];
-    __shared__ __align__(16) T a_lo[16 * PITCH];
-    __shared__ float row_m[16], row_inv[16];
-    __shared__ uint32_t row_pb[16], row_pe[16];
-    const uint32_t h = blockIdx.x, r0 = blockIdx.y * 16, tid = threadIdx.x;
+    constexpr int PITCH = kMergePitch;
+    extern __shared__ __align__(16) unsigned char merge_smem[];
+    T* w_s = reinterpret_cast<T*>(merge_smem);                       // [128][PITCH]
+    T* a_hi = w_s + size_t(kVDim) * PITCH;                           // [16][PITCH]
+    T* a_lo = a_hi + 16 * PITCH;                                     // [16][PITCH]
+    float* row_m = reinterpret_cast<float*>(a_lo + 16 * PITCH);
+    float* row_inv = row_m + 16;
+    uint32_t* row_pb = reinterpret_cast<uint32_t*>(row_inv + 16);
+    uint32_t* row_pe = row_pb + 16;
+    const uint32_t h = blockIdx.x, tid = threadIdx.x;
     const uint32_t warp = tid / 32, lane = tid % 32, g = lane / 4, t4 = lane % 4;
+    const uint32_t rt_begin = blockIdx.y * kMergeTilesPerBlock;
+    const uint32_t rt_end = min(rt_begin + kMergeTilesPerBlock, (rows + 15) / 16);
     auto rec_of = [&](uint32_t r, uint32_t p) -> const float* {
         const size_t idx = row_seg_begin ? (size_t(p) * H + h) : ((size_t(p) * rows + r) * H + h);
         return recs + idx * kPart;
     };
-    // prefetch this warp's W_UV fragments for the first k-steps while the merge runs
-    const T* wb = w_uv + (size_t(h) * kVDim + warp * 8 + g) * kRank + t4 * 2;
-    {
-        const uint32_t r = r0 + warp;                // warp <-> row
-        uint32_t pb = 0, pe = 0;
-        if (r < rows) {
-            if (row_seg_begin) { pb = row_seg_begin[r]; pe = row_seg_begin[r + 1]; }
-            else               { pb = 0; pe = n_parts; }
-        }
-        float M = -INFINITY;
-        for (uint32_t p = pb + lane; p < pe; p += 32) M = fmaxf(M, rec_of(r, p)[0]);
+    {   // stage W_UV_h: 128 rows x 64 chunks of 16 bytes, 16 chunks per thread, all in flight at once
+        const uint4* src = reinterpret_cast<const uint4*>(w_uv + size_t(h) * kVDim * kRank);
+        uint4 v[16];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-        float L = 0.0f;
-        if (M > -INFINITY)
-            for (uint32_t p = pb + lane; p < pe; p += 32) {
-                const float* rc = rec_of(r, p);
-                L = fmaf(exp2f(rc[0] - M), rc[1], L);
-            }
+        for (int i = 0; i < 16; i++) v[i] = src[tid + 512 * i];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-        if (lane == 0) {
-            row_m[warp] = M;
-            row_inv[warp] = L > 0.0f ? 1.0f / L : 0.0f;
-            row_pb[warp] = pb;
-            row_pe[warp] = pe;
+        for (int i = 0; i < 16; i++) {
+            const int c = tid + 512 * i, row = c / 64, ch = c % 64;
+            *reinterpret_cast<uint4*>(w_s + size_t(row) * PITCH + ch * 8) = v[i];
         }
     }
-    __syncthreads();
-    {   // thread -> row tid/32, dims (tid%32)*16 .. +15
-        const uint32_t rr = tid / 32, r = r0 + rr, d0 = (tid % 32) * 16;
-        const float M = row_m[rr], inv = row_inv[rr];
-        const uint32_t pb = row_pb[rr], pe = row_pe[rr];
-        float acc[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) acc[i] = 0.0f;
-        if (inv > 0.0f)
-            for (uint32_t p = pb; p < pe; p++) {
-                const float* rc = rec_of(r, p);
-                const float w = exp2f(rc[0] - M);
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const float2 v = *reinterpret_cast<const float2*>(rc + 2 + d0 + 2 * i);
-                    acc[2 * i] = fmaf(w, v.x, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(w, v.y, acc[2 * i + 1]);
-                }
-            }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float o0 = acc[2 * i] * inv, o1 = acc[2 * i + 1] * inv;
-            const T h0 = Elem<T>::from_f32(o0), h1 = Elem<T>::from_f32(o1);
-            *reinterpret_cast<uint32_t*>(a_hi + rr * PITCH + d0 + 2 * i) = Elem<T>::pack2(o0, o1);
-            *reinterpret_cast<uint32_t*>(a_lo + rr * PITCH + d0 + 2 * i) =
-                Elem<T>::pack2(o0 - Elem<T>::to_f32(h0), o1 - Elem<T>::to_f32(h1));
-        }
-    }
-    __syncthreads();
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const int mi = lane / 8, lr = lane % 8;
     const uint32_t hi_addr = static_cast<uint32_t>(__cvta_generic_to_shared(a_hi + ((mi % 2) * 8 + lr) * PITCH + (mi / 2) * 8));
     const uint32_t lo_addr = static_cast<uint32_t>(__cvta_generic_to_shared(a_lo + ((mi % 2) * 8 + lr) * PITCH + (mi / 2) * 8));
-#pragma unroll 8
-    for (int ks = 0; ks < kRank / 16; ks++) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(wb + ks * 16);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(wb + ks * 16 + 8);
-        uint32_t ah[4], al[4];
-        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(ah[0]), "=r"(ah[1]), "=r"(ah[2]), "=r"(ah[3]) : "r"(hi_addr + ks * 32));
-        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(al[0]), "=r"(al[1]), "=r"(al[2]), "=r"(al[3]) : "r"(lo_addr + ks * 32));
-        mma16816<T>(c, ah, b0, b1);
-        mma16816<T>(c, al, b0, b1);
+    // B fragments of outputs [8w, 8w+8) for two k-steps per ldmatrix.x4: matrices (k0-7, k8-15) of step s, then of step s+1
+    const uint32_t w_addr = static_cast<uint32_t>(__cvta_generic_to_shared(w_s + size_t(warp * 8 + lr) * PITCH + mi * 8));
+    for (uint32_t rt = rt_begin; rt < rt_end; rt++) {
+        const uint32_t r0 = rt * 16;
+        {
+            const uint32_t r = r0 + warp;                // warp <-> row
+            uint32_t pb = 0, pe = 0;
+            if (r < rows) {
+                if (row_seg_begin) { pb = row_seg_begin[r]; pe = row_seg_begin[r + 1]; }
+                else               { pb = 0; pe = n_parts; }
+            }
+            float M = -INFINITY;
+            for (uint32_t p = pb + lane; p < pe; p += 32) M = fmaxf(M, rec_of(r, p)[0]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+            float L = 0.0f;
+            if (M > -INFINITY)
+                for (uint32_t p = pb + lane; p < pe; p += 32) {
+                    const float* rc = rec_of(r, p);
+                    L = fmaf(exp2f(rc[0] - M), rc[1], L);
+                }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+            if (lane == 0) {
+                row_m[warp] = M;
+                row_inv[warp] = L > 0.0f ? 1.0f / L : 0.0f;
+                row_pb[warp] = pb;
+                row_pe[warp] = pe;
+            }
+        }
+        __syncthreads();                                 // also: W_UV staged (first tile), previous tile's MMAs done
+        {   // thread -> row tid/32, dims (tid%32)*16 .. +15
+            const uint32_t rr = tid / 32, r = r0 + rr, d0 = (tid % 32) * 16;
+            const float M = row_m[rr], inv = row_inv[rr];
+            const uint32_t pb = row_pb[rr], pe = row_pe[rr];
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+            if (inv > 0.0f)
+                for (uint32_t p = pb; p < pe; p++) {
+                    const float* rc = rec_of(r, p);
+                    const float w = exp2f(rc[0] - M);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float2 v = *reinterpret_cast<const float2*>(rc + 2 + d0 + 2 * i);
+                        acc[2 * i] = fmaf(w, v.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w, v.y, acc[2 * i + 1]);
+                    }
+                }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float o0 = acc[2 * i] * inv, o1 = acc[2 * i + 1] * inv;
+                const T h0 = Elem<T>::from_f32(o0), h1 = Elem<T>::from_f32(o1);
+                *reinterpret_cast<uint32_t*>(a_hi + rr * PITCH + d0 + 2 * i) = Elem<T>::pack2(o0, o1);
+                *reinterpret_cast<uint32_t*>(a_lo + rr * PITCH + d0 + 2 * i) =
+                    Elem<T>::pack2(o0 - Elem<T>::to_f32(h0), o1 - Elem<T>::to_f32(h1));
+            }
+        }
+        __syncthreads();
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+        for (int ks = 0; ks < kRank / 16; ks += 2) {
+            uint32_t bw[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(bw[0]), "=r"(bw[1]), "=r"(bw[2]), "=r"(bw[3]) : "r"(w_addr + ks * 32));
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                uint32_t ah[4], al[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(ah[0]), "=r"(ah[1]), "=r"(ah[2]), "=r"(ah[3]) : "r"(hi_addr + (ks + u) * 32));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(al[0]), "=r"(al[1]), "=r"(al[2]), "=r"(al[3]) : "r"(lo_addr + (ks + u) * 32));
+                mma16816<T>(c, ah, bw[2 * u], bw[2 * u + 1]);
+                mma16816<T>(c, al, bw[2 * u], bw[2 * u + 1]);
+            }
+        }
+        const int col = warp * 8 + t4 * 2;
+        if (r0 + g < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g) * H + h) * kVDim + col) = Elem<T>::pack2(c[0], c[1]);
+        if (r0 + g + 8 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g + 8) * H + h) * kVDim + col) = Elem<T>::pack2(c[2], c[3]);
+        __syncthreads();                                 // a_hi / a_lo / row_* are rewritten by the next tile
     }
-    const int col = warp * 8 + t4 * 2;
-    if (r0 + g < rows)
-        *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g) * H + h) * kVDim + col) = Elem<T>::pack2(c[0], c[1]);
-    if (r0 + g + 8 < rows)
-        *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g + 8) * H + h) * kVDim + col) = Elem<T>::pack2(c[2], c[3]);
 }
 
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
@@ -416,12 +448,19 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
 {
     if (rows == 0) return;
     if (!exported) {
-        dim3 grid16(H, (rows + 15) / 16);
+        static bool configured = false;
+        if (!configured) {
+            cudaFuncSetAttribute(merge_outproj_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
+            cudaFuncSetAttribute(merge_outproj_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
+            configured = true;
+        }
+        const uint32_t row_tiles = (rows + 15) / 16;
+        dim3 grid16(H, (row_tiles + kMergeTilesPerBlock - 1) / kMergeTilesPerBlock);
         if (dtype == 0)
-            merge_outproj_mma_kernel<__half><<<grid16, 512, 0, st>>>(
+            merge_outproj_mma_kernel<__half><<<grid16, 512, kMergeSmem, st>>>(
                 recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv), static_cast<__half*>(out), rows, H);
         else
-            merge_outproj_mma_kernel<__nv_bfloat16><<<grid16, 512, 0, st>>>(
+            merge_outproj_mma_kernel<__nv_bfloat16><<<grid16, 512, kMergeSmem, st>>>(
                 recs, row_seg_begin, n_parts, static_cast<const __nv_bfloat16*>(w_uv),
                 static_cast<__nv_bfloat16*>(out), rows, H);
         return;
