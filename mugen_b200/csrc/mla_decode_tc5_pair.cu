@@ -64,7 +64,7 @@ constexpr int M_LSUM = 2560;      // [3][64] floats: the other quarters' partial
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
-constexpr uint32_t COL_S = 256;     // N_QK partial score tiles x 32 columns
+constexpr uint32_t COL_S = 256;     // 2 buffers x N_QK partial score tiles x 32 columns
 
 constexpr int N_QK = 2, N_PV = 2;                   // pair MMAs issue quickly: two issuers each suffice
 constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 8);   // K producer, issuers, V producer, 8 softmax warps
@@ -74,7 +74,7 @@ constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 constexpr int PREFETCH_TILES = 4;
 
-enum { B_QFULL = 0, B_QEMPTY, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_SFULL, B_SEMPTY, B_PFULL, B_PEMPTY,
+enum { B_QFULL = 0, B_QEMPTY, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_SFULL0, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY,
        B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -321,8 +321,10 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         mbar_init(bar(B_VFULL1), 1);
         mbar_init(bar(B_VEMPTY0), N_PV);
         mbar_init(bar(B_VEMPTY1), N_PV);
-        mbar_init(bar(B_SFULL), N_QK);
-        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SFULL0), N_QK);
+        mbar_init(bar(B_SFULL1), N_QK);
+        mbar_init(bar(B_SEMPTY0), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SEMPTY1), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PEMPTY), N_PV);
         mbar_init(bar(B_OFULL), N_PV);
@@ -447,17 +449,17 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                         const long long a0_ = clock64();
                         ok = mbar_wait(bar(B_KFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status);
                         const long long a1_ = clock64();
-                        ok = ok && mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+                        ok = ok && mbar_wait(bar(B_SEMPTY0 + (t & 1)), ((t >> 1) & 1) ^ 1, abort_flag, status);
                         const long long a2_ = clock64();
                         tr_wait1 += a1_ - a0_; tr_wait2 += a2_ - a1_;
 #else
                         ok = mbar_wait(bar(B_KFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
-                             mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+                             mbar_wait(bar(B_SEMPTY0 + (t & 1)), ((t >> 1) & 1) ^ 1, abort_flag, status);
 #endif
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t b0 = st ? k1 : k0;
-                        const uint32_t d = tmem + COL_S + part * (TILE / 2);
+                        const uint32_t d = tmem + COL_S + (t & 1) * (N_QK * TILE / 2) + part * (TILE / 2);
                         if (elect_one()) {
 #pragma unroll
                             for (int c = 0; c < NSUB; c++) {
@@ -469,7 +471,7 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
                                                     (c == c_lo && k == 0) ? 0u : 1u);
                                 }
                             }
-                            tc_commit_pair(bar(B_SFULL));
+                            tc_commit_pair(bar(B_SFULL0 + (t & 1)));
                             tc_commit_pair(bar(B_KEMPTY0 + st));
                             if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
                         }
@@ -528,7 +530,8 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
         const uint32_t hl = 32 * (q4 % 2) + lane;             // head within this block's 64
         const uint32_t st_id = tid - (NUM_THREADS - SOFTMAX_THREADS);
         const uint32_t peer = rank ^ 1;
-        const uint32_t r_sempty = map_to_rank(bar(B_SEMPTY), 0), r_pfull = map_to_rank(bar(B_PFULL), 0);
+        const uint32_t r_sempty[2] = {map_to_rank(bar(B_SEMPTY0), 0), map_to_rank(bar(B_SEMPTY1), 0)};
+        const uint32_t r_pfull = map_to_rank(bar(B_PFULL), 0);
         const uint32_t r_synca[2] = {map_to_rank(bar(B_SYNCA0), peer), map_to_rank(bar(B_SYNCA1), peer)};
         const uint32_t r_syncb[2] = {map_to_rank(bar(B_SYNCB0), peer), map_to_rank(bar(B_SYNCB1), peer)};
         const uint32_t r_flag = map_to_rank(base + OFF_MISC + M_FLAG, peer);
@@ -572,21 +575,21 @@ decode_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_
             l_part = 0.0f;
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t par = t & 1;
-                wait_w(bar(B_SFULL), t & 1);
+                wait_w(bar(B_SFULL0 + par), (t >> 1) & 1);
                 uint32_t sv[16];
                 if (!fail) {
                     tc_fence_after();
                     uint32_t sw[16];
-                    tc_ld16(tmem + lane_base + COL_S + grp * 16, sv);
-                    tc_ld16(tmem + lane_base + COL_S + 32 + grp * 16, sw);
+                    tc_ld16(tmem + lane_base + COL_S + par * (N_QK * TILE / 2) + grp * 16, sv);
+                    tc_ld16(tmem + lane_base + COL_S + par * (N_QK * TILE / 2) + 32 + grp * 16, sw);
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {                       // orders only TMEM reads: no memory release needed
-                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY));
-                        else mbar_arrive_cluster_relaxed(r_sempty);
+                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY0 + par));
+                        else mbar_arrive_cluster_relaxed(r_sempty[par]);
                     }
                 } else {
 #pragma unroll
