@@ -48,7 +48,8 @@ enum { MLA_DTYPE_F16 = 0, MLA_DTYPE_BF16 = 1 };
  * src/model/ggml_types.h:12-40), plus BF16. */
 enum { MLA_W_F16 = 1, MLA_W_Q4_0 = 2, MLA_W_Q8_0 = 8, MLA_W_BF16 = 30 };
 
-enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2, MLA_KERNEL_TCGEN05_PAIR = 3 };
+enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2, MLA_KERNEL_TCGEN05_PAIR = 3,
+       MLA_KERNEL_TCGEN05_PAIR128 = 4 };
 
 /* Shape contract: the MLA fields of mugen::ModelConfig (src/core/model/transformer.h:65-79)
  * plus the paged-pool geometry the reference lacks (it keeps one contiguous

@@ -310,7 +310,9 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     int e;
     const bool timed = c->profiling && c->prof_used < c->prof_events.size();
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
-    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR)
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
+        e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
+    else if (c->kernel == MLA_KERNEL_TCGEN05_PAIR)
         e = mla::launch_decode_tc5_pair(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)
         e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmaps, layer, c->cfg.n_pages, m,
@@ -427,7 +429,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (cfg->page_tokens != 64) return fail(nullptr, MLA_ERR_UNSUPPORTED, "page_tokens must be 64");
     if (cfg->n_pages == 0 || cfg->max_seqs == 0) return fail(nullptr, MLA_ERR_INVALID, "n_pages and max_seqs must be > 0");
     if (cfg->dtype > MLA_DTYPE_BF16) return fail(nullptr, MLA_ERR_INVALID, "dtype must be MLA_DTYPE_F16 or MLA_DTYPE_BF16");
-    if (cfg->kernel > MLA_KERNEL_TCGEN05_PAIR) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
+    if (cfg->kernel > MLA_KERNEL_TCGEN05_PAIR128) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
 
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
@@ -459,10 +461,10 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     // 128-head groups go to the SM-pair kernel, other wide head counts fill the 64-row tcgen05
     // tiles of the single-block kernel, narrow ones map 1:1 onto m16n8k16
     c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
-              : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR
+              : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
               : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA;
     const uint32_t H = cfg->n_heads;
-    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR || c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
     else c->workers = std::max<uint32_t>(1, c->sm_count * 2 / ((H + 15) / 16));
 
@@ -504,6 +506,13 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
         if (int rc = make_tensor_maps(cp)) return bail(rc);
         if (int ce = mla::decode_tc5_pair_configure()) {
             cp->err = std::string("tcgen05 pair kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+            return bail(MLA_ERR_CUDA);
+        }
+    }
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) {
+        if (int rc = make_tensor_maps(cp)) return bail(rc);
+        if (int ce = mla::decode_tc5_pair128_configure()) {
+            cp->err = std::string("tcgen05 pair128 kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
             return bail(MLA_ERR_CUDA);
         }
     }
@@ -882,7 +891,7 @@ int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
 const char* mla_kernel_name(const mla_ctx* c)
 {
     if (!c) return "";
-    return c->kernel == MLA_KERNEL_TCGEN05_PAIR ? "tcgen05-pair" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
+    return c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? "tcgen05-pair128" : c->kernel == MLA_KERNEL_TCGEN05_PAIR ? "tcgen05-pair" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
 }
 
 int mla_read_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, void* host_out, void* stream)

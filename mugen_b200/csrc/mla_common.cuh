@@ -23,6 +23,7 @@ enum : uint32_t {
     ST_BAD_PAGE      = 1u << 1,   // attend: block-table entry outside the pool
     ST_WAIT_TIMEOUT  = 1u << 2,   // a bounded mbarrier wait gave up
     ST_BAD_SEGMENT   = 1u << 3,   // segment descriptor inconsistent
+    ST_BAD_ALIGNMENT = 1u << 4,   // dynamic shared memory did not start on the 1 KB boundary a kernel relies on
 };
 
 template <typename T> struct Elem;

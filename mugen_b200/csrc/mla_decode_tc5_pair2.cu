@@ -1,0 +1,877 @@
+// Split-KV absorbed MLA attention for 128-head groups on a PAIR of SMs, 128-token super-tiles
+// (thread-block cluster of 2, tcgen05.mma.cta_group::2), sm_100a.
+//
+// Same division of labour as mla_decode_tc5_pair.cu (each block: 64 heads, its 256 latent dims of
+// V, O^T for its dims x all 128 heads), but a tile is TWO pages and the pair's score MMA has
+// N = 128: block r stages the whole K of page r (the B operand's rows 64r .. 64r+63).  Measured on
+// B200 with four issuing warps, a cta_group::2 M128 N64 K16 MMA occupies the tensor pipe for 33
+// cycles and the N128 one for 44, so the 72 score MMAs of two pages (2,380 cycles) become 36
+// (1,580); with the 16 value MMAs (M256 N128 K16, 77 cycles each) a 128-token tile needs ~2,800
+// pipe cycles instead of ~3,600, which is below the time HBM needs to deliver it.
+//
+// Shared memory is exactly full (Q' 72 KB, K 72 KB, V 64 KB, P 16 KB, 3 KB of barriers and
+// scratch), so nothing is double-buffered as a whole.  Instead every K sub-tile [64 tokens][64 dims]
+// and every V buffer [page][128-dim chunk] has its own full/empty barrier pair: a sub-tile is
+// re-loaded for the next tile as soon as the MMAs that read it have completed, which leaves each
+// load a window of about one tile period minus its own use.  The dynamic shared segment must start
+// 1 KB-aligned because there is no slack to round up (checked; the status word says so if not).
+//
+// TMEM: O^T 2 x 128 columns; four partial score tiles of 64 columns, one per issuing warp (a warp
+// waits ~50-100 cycles per MMA it issues, so four of them are needed to keep the pipe busy).
+//
+// Warps: 0 K producer, 1-4 score issuers (sub-tiles {0,4,8} {1,5} {2,6} {3,7}), 5-6 value issuers
+// (one per chunk), 7 V producer + L2 prefetch, 8-15 softmax.  Softmax protocol, the cluster
+// rounds for the shared maximum and the bounded waits are those of mla_decode_tc5_pair.cu.
+#include <cuda.h>
+#ifdef MLA_TC5_TRACE
+#include <cstdio>
+#endif
+
+#include "mla_launch.h"
+
+namespace mla {
+
+namespace {
+
+constexpr int PAGES = 2;                            // pages per super-tile
+constexpr int TILE = PAGES * kPage;                 // 128 tokens
+constexpr int HG = 64;                              // heads per block (128 per pair)
+constexpr int NSUB = kRow / 64;                     // 9
+constexpr int SUB_BYTES = kPage * 128;              // 8,192: [64 tokens or heads][64 values]
+constexpr int Q_BYTES = NSUB * SUB_BYTES;           // 73,728
+constexpr int K_BYTES = NSUB * SUB_BYTES;           // 73,728: the whole K of this block's page
+constexpr int VBUF_BYTES = 2 * SUB_BYTES;           // 16,384: 64 tokens x 128 dims (one page, one chunk)
+constexpr int P_BYTES = HG * 128;                   // 8,192 per page
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;
+constexpr int OFF_V = OFF_K + K_BYTES;                      // [page][chunk]
+constexpr int OFF_P = OFF_V + PAGES * 2 * VBUF_BYTES;       // [page]
+constexpr int OFF_MISC = OFF_P + PAGES * P_BYTES;
+constexpr int MISC_BYTES = 3072;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES;           // 232,448 = all of it: no alignment slack
+static_assert(SMEM_BYTES == 232448, "shared-memory plan must fill the 227 KB exactly");
+
+// misc area layout (bytes from OFF_MISC)
+constexpr int M_BAR = 0;          // mbarriers, 8 B each
+constexpr int M_TMEM = 384;       // tmem base
+constexpr int M_ABORT = 388;
+constexpr int M_FLAG = 392;       // [2] "some head of the pair must move its maximum", by tile parity
+constexpr int M_ALPHA = 512;      // [2][128] floats: scale factor per head of the pair, by tile parity
+constexpr int M_HMAX = 1536;      // [4][64] floats: tile maximum of each token quarter per head
+constexpr int M_LSUM = 1536;      // [3][64] floats: the other quarters' partial sums at the epilogue (the same
+                                  // bytes as M_HMAX: a barrier of the softmax group separates the two uses)
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
+constexpr uint32_t COL_S = 256;     // 4 partial score tiles x 64 columns
+
+constexpr int N_QK = 4, N_PV = 2;
+constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 8);   // 512
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int PAIR_SOFTMAX_WARPS = 16;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+// A waiting thread sleeps in the barrier unit until the phase completes or this long, instead of
+// re-polling shared memory, whose bandwidth the MMA operand fetches need.
+#ifndef MLA_TRY_WAIT_HINT_NS
+#define MLA_TRY_WAIT_HINT_NS 20000
+#endif
+constexpr uint32_t TRY_WAIT_HINT_NS = MLA_TRY_WAIT_HINT_NS;
+#ifndef MLA_PAIR128_PREFETCH
+#define MLA_PAIR128_PREFETCH 2
+#endif
+constexpr int PREFETCH_TILES = MLA_PAIR128_PREFETCH;                   // L2 prefetch distance, in super-tiles
+
+enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KEMPTY + NSUB, B_VEMPTY = B_VFULL + 4,
+       B_SFULL = B_VEMPTY + 4, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
+static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this block) in block `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+// ---- mbarrier ------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// default semantics (release at block scope) on the twin block's barrier: what orders this block's
+// own shared-memory writes before the signal, without a cluster-wide release
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cta(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cta(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    if (mbar_try_cta(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_cta(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---- TMA (no multicast; .cta_group::2 only lets the completion land on the pair leader's barrier)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
+                                                 int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// ---- tcgen05, cta_group::2 -----------------------------------------------------------------
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// completion of all MMAs issued so far by this thread -> the barrier at this offset in BOTH blocks
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar), "h"(uint16_t(3)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// shared-memory matrix descriptor halves (128-byte swizzle, version 1); see mla_decode_tc5.cu
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+#ifdef MLA_TC5_TRACE
+#define TR_DECL(...) long long __VA_ARGS__
+#define TR_NOW(x) x = clock64()
+#define TR_ADD(acc, a, b) acc += (b) - (a)
+__device__ long long tr_buf[96];
+#define TR_EV(idx) do { if (blockIdx.x == 6 && blockIdx.y == 0 && t >= 50 && t < 53) tr_buf[(t - 50) * 32 + (idx)] = clock64(); } while (0)
+#else
+#define TR_EV(idx)
+#define TR_DECL(...)
+#define TR_NOW(x)
+#define TR_ADD(acc, a, b)
+#endif
+
+struct SegInfo {
+    uint32_t row, page_begin, n_pages, n_tiles, n_tok;
+};
+__device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
+    SegInfo s;
+    s.row = m.seg_row[seg];
+    s.page_begin = m.seg_page_begin[seg];
+    const uint32_t pe = m.seg_page_end[seg];
+    const uint32_t len = m.row_len[s.row];
+    const uint32_t tb = s.page_begin * kPage, te = min(len, pe * kPage);
+    s.n_tok = te > tb ? te - tb : 0;
+    s.n_pages = (s.n_tok + kPage - 1) / kPage;
+    s.n_tiles = (s.n_pages + PAGES - 1) / PAGES;      // super-tiles
+    return s;
+}
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __grid_constant__ CUtensorMap map_kv64,
+                          const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_page,
+                          uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
+                          float scale_log2, uint32_t* __restrict__ status)
+{
+    extern __shared__ __align__(1024) unsigned char sm[];
+    const uint32_t base = smem_u32(sm);
+    const uint32_t sQ = base + OFF_Q, sK = base + OFF_K, sV = base + OFF_V, sP = base + OFF_P;
+    const uint32_t sBar = base + OFF_MISC + M_BAR;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_ABORT);
+    volatile uint32_t* need_flag = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC + M_FLAG);
+    float* alpha_all = reinterpret_cast<float*>(sm + OFF_MISC + M_ALPHA);
+    float* half_max = reinterpret_cast<float*>(sm + OFF_MISC + M_HMAX);
+    float* l_other = reinterpret_cast<float*>(sm + OFF_MISC + M_LSUM);
+    auto bar = [&](int i) { return sBar + 8u * uint32_t(i); };
+
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t rank = cluster_rank();                 // 0 = pair leader (issues the MMAs)
+    const uint32_t worker = blockIdx.x / 2;
+    const uint32_t hpair = blockIdx.y * (2 * HG);        // first head of the pair's 128
+    const uint32_t h0 = hpair + rank * HG;               // first head of this block's 64
+    const uint32_t seg_begin = m.cta_seg_begin[worker], seg_end = m.cta_seg_begin[worker + 1];
+
+    // The swizzled operand tiles need 1 KB alignment and the plan leaves no room to round up.
+    // Both blocks of a pair see the same offset, so they take this exit together.
+    if ((base & 1023u) != 0) {
+        if (tid == 0) atomicOr(status, ST_BAD_ALIGNMENT);
+        return;
+    }
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        need_flag[0] = need_flag[1] = 0;
+        mbar_init(bar(B_QFULL), 1);
+        mbar_init(bar(B_QEMPTY), N_QK);
+        for (int c = 0; c < NSUB; c++) {
+            mbar_init(bar(B_KFULL + c), 1);
+            mbar_init(bar(B_KEMPTY + c), 1);
+        }
+        for (int v = 0; v < 4; v++) {
+            mbar_init(bar(B_VFULL + v), 1);
+            mbar_init(bar(B_VEMPTY + v), 1);
+        }
+        mbar_init(bar(B_SFULL), N_QK);
+        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_PEMPTY), N_PV);
+        mbar_init(bar(B_OFULL), N_PV);
+        mbar_init(bar(B_SYNCA0), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCA1), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCB0), PAIR_SOFTMAX_WARPS);
+        mbar_init(bar(B_SYNCB1), PAIR_SOFTMAX_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    // both blocks' barriers must exist before either sends a remote arrive or a TMA completion
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    tc_fence_after();
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+    // Page of super-tile j that block `r` stages as K (and whose tokens are columns 64r .. 64r+63 of
+    // the score tile).  A segment with an odd page count repeats its last page in the second half:
+    // finite data whose scores the softmax masks.
+    auto page_of = [&](const uint32_t* tbl, const SegInfo& s, uint32_t j, uint32_t r) -> uint32_t {
+        const uint32_t i = min(PAGES * j + r, s.n_pages - 1);
+        return tbl[i];
+    };
+
+    if (warp == 0) {
+        // ===================== TMA producer for Q' and K =====================
+        if (lane == 0) {
+            const uint32_t leader_qfull = map_to_rank(bar(B_QFULL), 0);
+            const uint32_t leader_kfull = map_to_rank(bar(B_KFULL), 0);
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
+                ok = mbar_wait_cta(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
+                if (!ok) break;
+                if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
+                tma_load_3d_pair(sQ, &map_q, leader_qfull, 0, int(s.row * H + h0), 0);      // all 9 sub-tiles at once
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                    uint32_t page = page_of(tbl, s, j, rank);
+                    if (page >= n_pages) {
+                        atomicOr(status, ST_BAD_PAGE);
+                        page = 0;
+                    }
+                    const int slot0 = int(page * kPage);
+#pragma unroll 1
+                    for (int c = 0; c < NSUB; c++) {
+                        if (c == 0) TR_EV(22);
+                        if (c == 5) TR_EV(31);
+                        ok = mbar_wait_cta(bar(B_KEMPTY + c), (t & 1) ^ 1, abort_flag, status);
+                        if (!ok) break;
+                        if (c == 5) TR_EV(23);
+                        if (c == 2) TR_EV(24);
+                        if (c == 3) TR_EV(25);
+                        if (c == 0) TR_EV(0);
+                        if (c == 4) TR_EV(1);
+                        if (c == 8) TR_EV(2);
+                        if (rank == 0) mbar_expect_tx(bar(B_KFULL + c), 2 * SUB_BYTES);
+                        if (c == 5) TR_EV(11);
+                        tma_load_3d_pair(sK + c * SUB_BYTES, &map_sub, leader_kfull + 8 * c, 64 * c, slot0, int(layer));
+                        if (c == 5) TR_EV(15);
+                    }
+                }
+                nseg++;
+            }
+        }
+    } else if (warp == N_QK + N_PV + 1) {
+        // ===================== TMA producer for V, and L2 prefetch of later pages =====================
+        if (lane == 0) {
+            const uint32_t leader_vfull = map_to_rank(bar(B_VFULL), 0);
+            uint32_t t = 0;
+            bool ok = true;
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
+                // each block pulls "its" page of the first tiles into L2; the twin's V loads of that page hit there
+                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) {
+                    const uint32_t pg = page_of(tbl, s, jj, rank);
+                    if (pg < n_pages) tma_prefetch_4d(&map_page, 0, int(pg * kPage), 0, int(layer));
+                }
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                    const uint32_t pf = (PREFETCH_TILES > 0 && j + PREFETCH_TILES < s.n_tiles) ? page_of(tbl, s, j + PREFETCH_TILES, rank) : 0xffffffffu;
+#pragma unroll 1
+                    for (uint32_t v = 0; v < 4; v++) {          // v = 2 * page + chunk, the order the issuers consume them
+                        uint32_t page = page_of(tbl, s, j, v / 2);
+                        if (page >= n_pages) page = 0;           // flagged by the K producer
+                        ok = mbar_wait_cta(bar(B_VEMPTY + v), (t & 1) ^ 1, abort_flag, status);
+                        if (!ok) break;
+                        TR_EV(3 + v);
+                        if (rank == 0) mbar_expect_tx(bar(B_VFULL + v), 2 * VBUF_BYTES);
+                        // all 64 tokens of the page, this block's 128 dims of chunk v%2 = sub-tiles 4*(v%2) + 2r, +1
+#ifdef MLA_PAIR128_ONE_MAP
+                        {
+                            const int c0 = 4 * int(v % 2) + 2 * int(rank);
+                            tma_load_3d_pair(sV + v * VBUF_BYTES, &map_sub, leader_vfull + 8 * v, 64 * c0, int(page * kPage), int(layer));
+                            tma_load_3d_pair(sV + v * VBUF_BYTES + SUB_BYTES, &map_sub, leader_vfull + 8 * v, 64 * (c0 + 1),
+                                             int(page * kPage), int(layer));
+                        }
+#else
+                        tma_load_4d_pair(sV + v * VBUF_BYTES, &map_kv64, leader_vfull + 8 * v, 0, int(page * kPage),
+                                         4 * int(v % 2) + 2 * int(rank), int(layer));
+#endif
+                    }
+                    if (pf < n_pages) tma_prefetch_4d(&map_page, 0, int(pf * kPage), 0, int(layer));
+                }
+            }
+        }
+    } else if (warp <= N_QK + N_PV) {
+        // ===================== MMA issuers (pair leader only) =====================
+        if (rank == 0) {
+            constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, 128, TILE, 0, 0);        // 64 head rows, 64 tokens per block
+            constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 256, 2 * HG, 1, 0);      // 128 dims per block
+            constexpr uint32_t HI = desc_hi(1024);
+            const bool is_qk = warp <= N_QK;
+            const uint32_t part = is_qk ? warp - 1 : warp - 1 - N_QK;
+            const uint32_t qk_a = desc_lo(sQ, 16), qk_b = desc_lo(sK, 16);
+            const uint32_t pv_a = desc_lo(sV, SUB_BYTES), pv_b = desc_lo(sP, 16);
+            uint32_t t = 0, nseg = 0;
+            bool ok = true;
+            TR_DECL(tr_a = 0, tr_b = 0, tr_i = 0, c0 = 0, c1 = 0, c2 = 0, tr_start = clock64());
+            for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
+                const SegInfo s = load_seg(m, seg);
+                if (s.n_tiles == 0) continue;
+                if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
+                    if (is_qk) {
+                        // sub-tiles part, part+4 (, part+8): partial scores into this warp's own 64 columns
+                        TR_NOW(c0);
+                        ok = mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
+                        TR_NOW(c1);
+                        TR_ADD(tr_a, c0, c1);
+                        if (part == 0 && lane == 0) TR_EV(7);
+                        if (!ok) break;
+                        const uint32_t d = tmem + COL_S + part * (TILE / 2);
+#pragma unroll 1
+                        for (uint32_t c = part; c < uint32_t(NSUB); c += N_QK) {
+                            TR_NOW(c0);
+                            ok = mbar_wait(bar(B_KFULL + c), t & 1, abort_flag, status);
+                            TR_NOW(c1);
+                            TR_ADD(tr_b, c0, c1);
+                            if (part == 0 && lane == 0) TR_EV(8 + c / 4);
+                            if (!ok) break;
+                            tc_fence_after();
+                            if (elect_one()) {
+#pragma unroll
+                                for (int k = 0; k < 4; k++)
+                                    tc_mma_pair(d, qk_a + ((c * SUB_BYTES + k * 32) >> 4), HI, qk_b + ((c * SUB_BYTES + k * 32) >> 4),
+                                                HI, IDESC_QK, (c == part && k == 0) ? 0u : 1u);
+                                tc_commit_pair(bar(B_KEMPTY + c));
+                                if (c + N_QK >= uint32_t(NSUB)) {      // same thread as the MMAs it covers
+                                    tc_commit_pair(bar(B_SFULL));
+                                    if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
+                                }
+                            }
+                            __syncwarp();
+                            TR_NOW(c2);
+                            TR_ADD(tr_i, c1, c2);
+                            if (part == 0 && lane == 0) TR_EV(26 + c / 4);
+                        }
+                    } else {
+                        // chunk `part` of O^T += V^T P^T over the tile's two pages
+                        TR_NOW(c0);
+                        ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+                        TR_NOW(c1);
+                        TR_ADD(tr_a, c0, c1);
+                        if (part == 0 && lane == 0) TR_EV(12);
+#pragma unroll 1
+                        for (uint32_t pg = 0; pg < uint32_t(PAGES) && ok; pg++) {
+                            const uint32_t v = 2 * pg + part;
+                            TR_NOW(c0);
+                            ok = mbar_wait(bar(B_VFULL + v), t & 1, abort_flag, status);
+                            TR_NOW(c1);
+                            TR_ADD(tr_b, c0, c1);
+                            if (part == 0 && lane == 0) TR_EV(13 + pg);
+                            if (!ok) break;
+                            tc_fence_after();
+                            const uint32_t fresh = (j == 0 && pg == 0) ? 0u : 1u;
+                            if (elect_one()) {
+#pragma unroll
+                                for (int k = 0; k < kPage / 16; k++)
+                                    tc_mma_pair(tmem + COL_O + part * (2 * HG), pv_a + ((v * VBUF_BYTES + k * 2048) >> 4), HI,
+                                                pv_b + ((pg * P_BYTES + k * 32) >> 4), HI, IDESC_PV, k == 0 ? fresh : 1u);
+                                tc_commit_pair(bar(B_VEMPTY + v));
+                                if (pg + 1 == uint32_t(PAGES)) {
+                                    tc_commit_pair(bar(B_PEMPTY));
+                                    if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_OFULL));
+                                }
+                            }
+                            __syncwarp();
+                            TR_NOW(c2);
+                            TR_ADD(tr_i, c1, c2);
+                            if (part == 0 && lane == 0) TR_EV(29 + pg);
+                        }
+                    }
+                }
+                nseg++;
+            }
+#ifdef MLA_TC5_TRACE
+            if (blockIdx.x == 6 && blockIdx.y == 0 && lane == 0 && (part == 0))
+                printf("[%s issuer] tiles %u total %lld wait_%s %lld wait_%s %lld issue %lld\n", is_qk ? "qk" : "pv", t,
+                       clock64() - tr_start, is_qk ? "sempty" : "pfull", tr_a, is_qk ? "kfull" : "vfull", tr_b, tr_i);
+#endif
+        }
+    } else {
+        // ===================== softmax / correction / epilogue (both blocks, 8 warps) =====================
+        // S of a pair MMA with 64 rows per block: head row r sits in TMEM lane r (tokens of the first
+        // page) and lane 64+r (second page), 64 columns each.  Two warps share each lane quarter and
+        // split its columns, so a thread owns (head, 32 tokens): token quarter tq = 2*page + group.
+        const uint32_t sw_id = warp - (2 + N_QK + N_PV);      // 0..7
+        const uint32_t grp = sw_id / 4;                       // column group within the lane quarter
+        const uint32_t q4 = warp % 4;
+        const uint32_t lane_base = (q4 * 32u) << 16;
+        const uint32_t half = q4 / 2;                         // page within the tile
+        const uint32_t tq = 2 * half + grp;                   // tokens 32*tq .. 32*tq+31 of the tile
+        const uint32_t hl = 32 * (q4 % 2) + lane;             // head within this block's 64
+        const uint32_t st_id = tid - (NUM_THREADS - SOFTMAX_THREADS);
+        const uint32_t peer = rank ^ 1;
+        const uint32_t r_sempty = map_to_rank(bar(B_SEMPTY), 0);
+        const uint32_t r_pfull = map_to_rank(bar(B_PFULL), 0);
+        const uint32_t r_synca[2] = {map_to_rank(bar(B_SYNCA0), peer), map_to_rank(bar(B_SYNCA1), peer)};
+        const uint32_t r_syncb[2] = {map_to_rank(bar(B_SYNCB0), peer), map_to_rank(bar(B_SYNCB1), peer)};
+        const uint32_t r_flag = map_to_rank(base + OFF_MISC + M_FLAG, peer);
+        const uint32_t r_alpha = map_to_rank(base + OFF_MISC + M_ALPHA, peer);
+        float m_used = -INFINITY, l_part = 0.0f;
+        uint32_t t = 0, nseg = 0, nb[2] = {0, 0};             // nb: uses of SYNCB[par] so far
+        bool fail = false;
+        auto wait_w = [&](uint32_t b, uint32_t parity) {              // completion of tensor-core / TMA work
+            if (!fail) fail = !mbar_wait_cta(b, parity, abort_flag, status);
+            fail = __any_sync(0xffffffffu, fail);
+        };
+        auto wait_x = [&](uint32_t b, uint32_t parity) {              // rounds that carry the twin's DSMEM writes
+            if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
+            fail = __any_sync(0xffffffffu, fail);
+        };
+        auto group_or = [&](bool pred) -> bool {              // barrier over this block's softmax threads + OR
+            uint32_t r;
+            asm volatile(
+                "{\n.reg .pred pi, po;\n"
+                "setp.ne.b32 pi, %1, 0;\n"
+                "barrier.cta.red.or.pred po, 1, 256, pi;\n"
+                "selp.u32 %0, 1, 0, po;\n}\n"
+                : "=r"(r) : "r"(uint32_t(pred)) : "memory");
+            return r != 0;
+        };
+        bool stop = false;
+        TR_DECL(tr_sfull = 0, tr_ld = 0, tr_exp = 0, tr_synca = 0, tr_slow = 0, tr_pempty = 0, tr_pw = 0, c0 = 0, c1 = 0, c2 = 0,
+                c3 = 0, c4 = 0, c5 = 0, c6 = 0, c7 = 0, tr_start = clock64(), tr_epi = 0);
+        [[maybe_unused]] uint32_t n_slow = 0;
+        for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
+            const SegInfo s = load_seg(m, seg);
+            if (s.n_tiles == 0) {
+                // nothing to attend: each block writes its 256 dims of every head, and (m, l) of its own heads
+                for (uint32_t h = 0; h < 2 * HG; h++) {
+                    if (hpair + h >= H) break;
+                    float* rc = recs + (size_t(seg) * H + hpair + h) * kPart;
+                    const uint32_t dim = (st_id / 128) * 256 + rank * 128 + (st_id % 128);
+                    rc[2 + dim] = 0.0f;
+                    if (st_id == 0 && h / HG == rank) { rc[0] = -INFINITY; rc[1] = 0.0f; }
+                }
+                continue;
+            }
+            m_used = -INFINITY;
+            l_part = 0.0f;
+            for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
+                const uint32_t par = t & 1;
+                TR_NOW(c0);
+                wait_w(bar(B_SFULL), t & 1);
+                TR_NOW(c1);
+                TR_ADD(tr_sfull, c0, c1);
+                if (st_id == 0) TR_EV(16);
+                uint32_t sv[32];
+                if (!fail) {
+                    tc_fence_after();
+                    {
+                        uint32_t sw[32];
+                        tc_ld32(tmem + lane_base + COL_S + grp * 32, sv);
+                        tc_ld32(tmem + lane_base + COL_S + (TILE / 2) + grp * 32, sw);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    }
+#pragma unroll 1
+                    for (int p = 2; p < N_QK; p++) {
+                        uint32_t sw[32];
+                        tc_ld32(tmem + lane_base + COL_S + p * (TILE / 2) + grp * 32, sw);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {                       // orders only TMEM reads: no memory release needed
+                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY));
+                        else mbar_arrive_cluster_relaxed(r_sempty);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sv[i] = 0u;
+                }
+                TR_NOW(c2);
+                TR_ADD(tr_ld, c1, c2);
+                if (st_id == 0) TR_EV(17);
+                const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float v = __uint_as_float(sv[i]) * scale_log2;
+                    v = (tq * 32 + uint32_t(i) < valid) ? v : -INFINITY;
+                    sv[i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+                // does any head of the pair have to move its reference maximum on this tile?
+                const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
+                const bool warp_need = __any_sync(0xffffffffu, need);
+                if (lane == 0 && !fail) {
+                    if (warp_need) {
+                        atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
+                        asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
+                        mbar_arrive_local(bar(B_SYNCA0 + par));
+                        mbar_arrive_cluster(r_synca[par]);
+                    } else {
+                        mbar_arrive_cta(bar(B_SYNCA0 + par));
+                        mbar_arrive_cluster_relaxed(r_synca[par]);
+                    }
+                }
+                // optimistic: exponentials against the current maximum while the cluster round is in
+                // flight; they stand unless some head of the pair raised the flag
+                float sum = 0.0f;
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
+                    const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                    sum += p0 + p1;
+                    pk[i / 2] = Elem<T>::pack2(p0, p1);
+                }
+                TR_NOW(c3);
+                TR_ADD(tr_exp, c2, c3);
+                if (st_id == 0) TR_EV(18);
+                wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
+                if (group_or(fail)) { stop = true; break; }
+                TR_NOW(c4);
+                TR_ADD(tr_synca, c3, c4);
+                if (st_id == 0) TR_EV(19);
+                const bool slow = need_flag[par] != 0;
+                if (slow) {
+                    // exchange the token quarters' maxima inside the block, decide per head, publish the
+                    // scale factors to both blocks, and redo the exponentials
+                    float alpha = 1.0f;
+                    half_max[tq * HG + hl] = mx;
+                    group_or(false);
+                    const float mrow = fmaxf(fmaxf(half_max[hl], half_max[HG + hl]), fmaxf(half_max[2 * HG + hl], half_max[3 * HG + hl]));
+                    if (j == 0) { m_used = mrow; alpha = 0.0f; }
+                    else if (mrow > m_used + RESCALE_THRESHOLD) { alpha = fast_ex2(m_used - mrow); m_used = mrow; }
+                    if (tq == 0) {
+                        alpha_all[par * 128 + rank * HG + hl] = alpha;
+                        asm volatile("st.relaxed.cluster.shared::cluster.f32 [%0], %1;\n"
+                                     ::"r"(r_alpha + 4 * (par * 128 + rank * HG + hl)), "f"(alpha) : "memory");
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive_local(bar(B_SYNCB0 + par));
+                        mbar_arrive_cluster(r_syncb[par]);
+                    }
+                    wait_x(bar(B_SYNCB0 + par), nb[par] & 1);
+                    nb[par]++;
+                    l_part *= alpha;
+                    sum = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
+                        const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                        sum += p0 + p1;
+                        pk[i / 2] = Elem<T>::pack2(p0, p1);
+                    }
+                }
+                l_part += sum;
+                // PV of the previous tile must be complete: O is stable and P is free
+                TR_NOW(c5);
+                TR_ADD(tr_slow, c4, c5);
+                wait_w(bar(B_PEMPTY), (t - 1) & 1);
+                TR_NOW(c6);
+                TR_ADD(tr_pempty, c5, c6);
+                if (st_id == 0) TR_EV(20);
+                if (fail) continue;            // carried to the next barrier
+                tc_fence_after();
+                if (slow && j > 0) {
+                    // O^T[this block's dims][128 heads] *= alpha[head]; each warp group takes one chunk
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t o[32];
+                        const uint32_t col = COL_O + grp * 128 + c * 32;
+                        tc_ld32(tmem + lane_base + col, o);
+                        tc_wait_ld();
+                        const float* al = alpha_all + par * 128 + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * al[i]);
+                        tc_st32(tmem + lane_base + col, o);
+                    }
+                    tc_wait_st();
+                }
+                {
+                    // row hl of the page's K-major swizzled P tile, this thread's 32 tokens = 16-byte chunks 4*grp .. 4*grp+3
+                    unsigned char* prow = sm + OFF_P + half * P_BYTES + hl * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                        *reinterpret_cast<uint4*>(prow + (((4 * grp + ch) ^ (hl & 7)) << 4)) = v;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive_cta(bar(B_PFULL));
+                    else mbar_arrive_remote(r_pfull);
+                }
+                // the flag of this parity is next written two tiles from now: clear it once every
+                // thread of the block has read it (they all passed the barrier of the slow path)
+                if (st_id == 0 && slow) need_flag[par] = 0;
+                TR_NOW(c7);
+                TR_ADD(tr_pw, c6, c7);
+                if (st_id == 0) TR_EV(21);
+                if (slow) n_slow++;
+            }
+            if (stop) break;
+            // ---- epilogue: O^T (this block's 256 dims x 128 heads) -> acc[head][dim]; (m, l) of own heads
+            TR_NOW(c0);
+            wait_w(bar(B_OFULL), nseg & 1);
+            group_or(false);                   // the maxima scratch is free: its bytes now carry the partial sums
+            if (tq != 0) l_other[(tq - 1) * HG + hl] = l_part;
+            if (group_or(fail)) { stop = true; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {                      // warp group `grp` owns chunk `grp`
+                uint32_t o[32];
+                tc_ld32(tmem + lane_base + COL_O + grp * 128 + c * 32, o);
+                tc_wait_ld();
+                const uint32_t dim = grp * 256 + rank * 128 + q4 * 32 + lane;
+                const uint32_t hb = hpair + c * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (hb + i < H) recs[(size_t(seg) * H + hb + i) * kPart + 2 + dim] = __uint_as_float(o[i]);
+                }
+            }
+            if (tq == 0 && h0 + hl < H) {
+                float* rc = recs + (size_t(seg) * H + h0 + hl) * kPart;
+                rc[0] = m_used;
+                rc[1] = l_part + l_other[hl] + l_other[HG + hl] + l_other[2 * HG + hl];
+            }
+            tc_fence_before();
+            group_or(false);                   // the scratch is reused by the next segment
+            nseg++;
+            TR_NOW(c1);
+            TR_ADD(tr_epi, c0, c1);
+        }
+#ifdef MLA_TC5_TRACE
+        if (blockIdx.x == 6 && blockIdx.y == 0 && st_id == 0)
+            printf("[softmax] tiles %u slow %u segs %u total %lld: sfull %lld ld %lld exp %lld synca %lld slowpath %lld pempty %lld pwrite %lld epilogue %lld\n",
+                   t, n_slow, nseg, clock64() - tr_start, tr_sfull, tr_ld, tr_exp, tr_synca, tr_slow, tr_pempty, tr_pw, tr_epi);
+#endif
+    }
+
+    // Neither block may leave while its twin can still signal its barriers, write its scratch or
+    // feed a pair MMA from its shared memory.
+    tc_fence_before();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+#ifdef MLA_TC5_TRACE
+    if (blockIdx.x == 6 && blockIdx.y == 0 && tid == 0) {
+        const char* names[32] = {"K0 issue", "K4 issue", "K8 issue", "V0 issue", "V1 issue", "V2 issue", "V3 issue", "QK sempty", "QK kfull0",
+                                 "QK kfull4", "QK kfull8", "K5 expected", "PV pfull", "PV vfull0", "PV vfull2", "K5 issued", "SM sfull", "SM ld", "SM exp",
+                                 "SM synca", "SM pempty", "SM pfull", "K0 wait", "K5 waited", "K2 issue", "K3 issue", "QK done0", "QK done4",
+                                 "QK done8", "PV done0", "PV done1", "K5 begin"};
+        const long long o = tr_buf[16];
+        for (int tt = 0; tt < 3; tt++)
+            for (int i = 0; i < 32; i++)
+                if (names[i][0] != '-') printf("EV t=%d %-10s %lld\n", 50 + tt, names[i], tr_buf[tt * 32 + i] - o);
+    }
+#endif
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+}  // namespace
+
+int decode_tc5_pair128_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(decode_tc5_pair128_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(decode_tc5_pair128_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES);
+    return int(e);
+}
+
+// tmaps: [0] pool, box 64 values x 64 tokens (one K sub-tile); [4] pool whole-row view, box 64 tokens x 2 chunks (V);
+// [5] absorbed queries, box 64 rows x 9 chunks; [6] pool whole-row view, box 64 tokens x 9 chunks (L2 prefetch of a page).
+int launch_decode_tc5_pair128(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
+                              float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
+{
+    if (m.ctas == 0) return 0;
+    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);
+    const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
+    dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
+    if (dtype == 0)
+        decode_tc5_pair128_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[4], maps[5], maps[6], layer, n_pages,
+                                                                                m, recs, H, scale_log2, status);
+    else
+        decode_tc5_pair128_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[4], maps[5], maps[6], layer,
+                                                                                       n_pages, m, recs, H, scale_log2, status);
+    return int(cudaGetLastError());
+}
+
+}  // namespace mla
