@@ -30,6 +30,9 @@ struct LayerW {
     void* w_uv = nullptr;
     void* norm = nullptr;
     bool set = false;
+    // W_UV as ([H*128 outputs][512 dims]) with a box of 64 dims x 128 outputs, for the tcgen05 merge kernel
+    alignas(64) CUtensorMap w_uv_map;
+    bool has_map = false;
 };
 
 struct MetaBuf {
@@ -300,6 +303,9 @@ int run_append(mla_ctx* c, uint32_t layer, const void* kv_a, cudaStream_t st)
     return MLA_OK;
 }
 
+int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, void* out,
+              float* exported, uint32_t rows, cudaStream_t st);
+
 // absorb -> split-KV attention -> merge (+ W_UV, or export of the merged partial state)
 int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st)
 {
@@ -322,10 +328,59 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
                                    c->recs, H, c->status_dev, st);
     if (e != 0) return fail(c, MLA_ERR_CUDA, std::string("attention launch: ") + cudaGetErrorString(cudaError_t(e)));
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used++].second, st));
-    mla::launch_merge(int(c->cfg.dtype), c->recs, m.row_seg_begin, 0, c->layers[layer].w_uv, out, exported,
-                      m.rows, H, st);
+    if (int rc = run_merge(c, layer, c->recs, m.row_seg_begin, 0, out, exported, m.rows, st)) return rc;
     c->launches += 3;
     CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda.
+TensorMapEncodeFn tensor_map_encoder()
+{
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    return reinterpret_cast<TensorMapEncodeFn>(fn);
+}
+
+int make_weight_map(mla_ctx* c, uint32_t layer)
+{
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const CUtensorMapDataType dt = c->cfg.dtype == MLA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const cuuint64_t dims[2] = {cuuint64_t(mla::kRank), cuuint64_t(c->cfg.n_heads) * mla::kVDim};
+    const cuuint64_t strides[1] = {cuuint64_t(mla::kRank) * 2};
+    const cuuint32_t box[2] = {64, cuuint32_t(mla::kVDim)};
+    const cuuint32_t estr[2] = {1, 1};
+    LayerW& lw = c->layers[layer];
+    const CUresult r = enc(&lw.w_uv_map, dt, 2, lw.w_uv, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(W_UV) failed with code " + std::to_string(int(r)));
+    lw.has_map = true;
+    return MLA_OK;
+}
+
+// merge of the partial states + W_UV: tensor-core kernel, or the scalar one when the merged state is exported
+int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, void* out,
+              float* exported, uint32_t rows, cudaStream_t st)
+{
+    const LayerW& lw = c->layers[layer];
+    if (!exported && lw.has_map) {
+        const int e = mla::launch_merge_tc5(int(c->cfg.dtype), recs, row_seg_begin, n_parts, &lw.w_uv_map, out, rows,
+                                            c->cfg.n_heads, c->status_dev, st);
+        if (e != 0) return fail(c, MLA_ERR_CUDA, std::string("merge launch: ") + cudaGetErrorString(cudaError_t(e)));
+        return MLA_OK;
+    }
+    mla::launch_merge(int(c->cfg.dtype), recs, row_seg_begin, n_parts, lw.w_uv, out, exported, rows, c->cfg.n_heads, st);
     return MLA_OK;
 }
 
@@ -509,6 +564,10 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
             return bail(MLA_ERR_CUDA);
         }
     }
+    if (int ce = mla::merge_tc5_configure()) {
+        cp->err = std::string("tcgen05 merge kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
+    }
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) {
         if (int rc = make_tensor_maps(cp)) return bail(rc);
         if (int ce = mla::decode_tc5_pair128_configure()) {
@@ -586,6 +645,7 @@ int mla_set_layer_weights(mla_ctx* c, uint32_t layer, const void* w_uk, const vo
     if (int e = decode_weights(c, w_uv, w_type, H * mla::kVDim, buf)) return e;
     CU_TRY(c, cudaMemcpy(c->layers[layer].w_uv, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
     CU_TRY(c, cudaMemcpy(c->layers[layer].norm, kv_norm, mla::kRank * 2, cudaMemcpyHostToDevice));
+    if (int e = make_weight_map(c, layer)) return e;
     c->layers[layer].set = true;
     return MLA_OK;
 }
@@ -767,8 +827,8 @@ int mla_merge_partials(mla_ctx* c, uint32_t layer, uint32_t n_parts, uint32_t ro
 {
     if (!c || !partials || !out || n_parts == 0) return fail(c, MLA_ERR_INVALID, "null argument");
     if (int e = check_layer(c, layer, true)) return e;
-    mla::launch_merge(int(c->cfg.dtype), partials, nullptr, n_parts, c->layers[layer].w_uv, out, nullptr, rows,
-                      c->cfg.n_heads, static_cast<cudaStream_t>(stream));
+    if (int rc = run_merge(c, layer, partials, nullptr, n_parts, out, nullptr, rows, static_cast<cudaStream_t>(stream)))
+        return rc;
     c->launches += rows ? 1 : 0;
     CU_TRY(c, cudaGetLastError());
     return MLA_OK;

@@ -44,4 +44,10 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
                   cudaStream_t st);
 
+// The same merge + projection on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the
+// layer's W_UV, [H*128 outputs][512 dims], box 64 dims x 128 outputs, 128-byte swizzle.
+int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, const void* w_map,
+                     void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st);
+int merge_tc5_configure();
+
 }  // namespace mla

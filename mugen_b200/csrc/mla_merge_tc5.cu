@@ -1,0 +1,372 @@
+// Merge of split-KV partial states + W_UV projection on the 5th-generation tensor cores, sm_100a.
+//
+//   o_c[row][512] = sum_p 2^(m_p - M) acc_p / sum_p 2^(m_p - M) l_p        (float, per head)
+//   out[row][128] = o_c . W_UV_h^T
+//
+// One block per (head, group of 64 query rows).  W_UV_h (128 x 512, 128 KB) lands in shared memory
+// by TMA as eight K-major sub-tiles [128 outputs][64 dims] with the 128-byte swizzle, while the
+// threads reduce the partial states.  o_c is split into hi = T(o) and lo = T(o - hi) (together ~16
+// mantissa bits for bf16, ~22 for fp16, so the float state is not rounded to the storage type
+// before the projection) and written to shared memory in the same swizzled K-major layout; the
+// projection is 2 x 32 tcgen05.mma M=64 N=128 K=16 (hi and lo against the same W sub-tiles) into
+// 128 TMEM columns.  The 512 dims are processed in two halves so that the second half's reduction
+// (global loads) overlaps the first half's MMAs and the operand buffers stay at 64 KB.  The
+// reduction itself is one running-maximum sweep over a row's parts with whole-line warp accesses.
+//
+// The mma.sync version of this step (merge_outproj_mma_kernel) re-reads the operands from shared
+// memory once per warp and spends ~40 us per layer at batch 64; here every operand byte is read
+// once by the tensor core.
+#include <cuda.h>
+#ifdef MLA_TC5_TRACE
+#include <cstdio>
+#define MTR(i) do { if (tid == 0 && blockIdx.x == 5) mtr[i] = clock64(); } while (0)
+#else
+#define MTR(i)
+#endif
+
+#include "mla_launch.h"
+
+namespace mla {
+
+namespace {
+
+constexpr int MT = 64;                         // query rows per block
+constexpr int W_SUB = kVDim * 128;             // 16,384: [128 outputs][64 dims]
+constexpr int W_BYTES = (kRank / 64) * W_SUB;  // 131,072
+constexpr int A_SUB = MT * 128;                // 8,192: [64 rows][64 dims]
+constexpr int A_HALF = 4 * A_SUB;              // 32,768: 256 dims of hi (or lo)
+constexpr int OFF_W = 0;
+constexpr int OFF_AHI = OFF_W + W_BYTES;
+constexpr int OFF_ALO = OFF_AHI + A_HALF;
+constexpr int OFF_MISC = OFF_ALO + A_HALF;     // 196,608
+constexpr int M_BAR = 0;                       // [0] W landed, [1] MMAs complete
+constexpr int M_TMEM = 16;
+constexpr int M_FAIL = 20;
+constexpr int MISC_BYTES = 64;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // + slack to round the base up to 1 KB
+constexpr int NUM_THREADS = 512;
+constexpr uint32_t TMEM_COLS = 128;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded: gives up after about two seconds, raises the status bit and tells the block through `fail_flag`
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* fail_flag, uint32_t* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*fail_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *fail_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor halves (K-major, 128-byte swizzle, 8-row groups 1 KB apart)
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float* __restrict__ recs,
+                         const uint32_t* __restrict__ row_seg_begin, uint32_t n_parts, T* __restrict__ out,
+                         uint32_t rows, uint32_t H, uint32_t* __restrict__ status)
+{
+    extern __shared__ unsigned char merge_tc5_smem[];
+    const uint32_t raw = smem_u32(merge_tc5_smem);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* sm = merge_tc5_smem + (base - raw);
+    const uint32_t sW = base + OFF_W, sAhi = base + OFF_AHI, sAlo = base + OFF_ALO;
+    const uint32_t bar_w = base + OFF_MISC + M_BAR, bar_mma = bar_w + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
+    volatile int* fail_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_FAIL);
+
+    const uint32_t h = blockIdx.x, tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t r0 = blockIdx.y * MT;
+    auto rec_of = [&](uint32_t r, uint32_t p) -> const float* {
+        const size_t idx = row_seg_begin ? (size_t(p) * H + h) : ((size_t(p) * rows + r) * H + h);
+        return recs + idx * kPart;
+    };
+
+#ifdef MLA_TC5_TRACE
+    long long mtr[12] = {0};
+#endif
+    MTR(0);
+    if (tid == 0) {
+        *fail_flag = 0;
+        mbar_init(bar_w, 1);
+        mbar_init(bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    MTR(1);
+    MTR(2);
+
+    if (tid == 0) {                                       // W_UV_h: eight boxes of 64 dims x 128 outputs
+        mbar_expect_tx(bar_w, W_BYTES);
+#pragma unroll 1
+        for (int s = 0; s < kRank / 64; s++) tma_load_2d(sW + s * W_SUB, &map_w, bar_w, 64 * s, int(h) * kVDim);
+    }
+
+    // Reduction of the partial states, one warp per four rows, two rows at a time.  A lane owns dims
+    // 64*k + 2*lane (+1), k = 0..3, of the current half: a warp load covers 256 contiguous bytes of
+    // a state record and a warp store one whole 128-byte operand row.  Parts are taken four at a
+    // time with the usual running-maximum update, so the (m, l) pass and the accumulation are one
+    // sweep and a row with up to four parts costs a single round trip to memory.
+    constexpr uint32_t IDESC = instr_desc(Fmt<T>::v, MT, kVDim);
+    bool ok = true;
+    uint32_t pb4[4], pe4[4];                              // part ranges of this warp's four rows
+#pragma unroll
+    for (int x = 0; x < 4; x++) {
+        const uint32_t rw = r0 + 4 * warp + x;
+        pb4[x] = pe4[x] = 0;
+        if (rw < rows) {
+            if (row_seg_begin) { pb4[x] = row_seg_begin[rw]; pe4[x] = row_seg_begin[rw + 1]; }
+            else               { pb4[x] = 0; pe4[x] = n_parts; }
+        }
+    }
+#pragma unroll 1
+    for (int kh = 0; kh < 2; kh++) {
+#pragma unroll 1
+        for (int pr = 0; pr < 2; pr++) {
+            uint32_t p[2], pe[2], rw[2];
+            float M[2], L[2], acc[2][8];
+#pragma unroll
+            for (int x = 0; x < 2; x++) {
+                rw[x] = r0 + 4 * warp + 2 * pr + x;
+                p[x] = pr == 0 ? pb4[x] : pb4[2 + x];
+                pe[x] = pr == 0 ? pe4[x] : pe4[2 + x];
+                M[x] = -INFINITY;
+                L[x] = 0.0f;
+#pragma unroll
+                for (int k = 0; k < 8; k++) acc[x][k] = 0.0f;
+            }
+            while (p[0] < pe[0] || p[1] < pe[1]) {
+                float2 ml[2][4], v[2][4][4];
+#pragma unroll
+                for (int x = 0; x < 2; x++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const bool on = p[x] + i < pe[x];
+                        const float* rc = rec_of(rw[x], on ? p[x] + i : 0);
+                        ml[x][i] = on ? *reinterpret_cast<const float2*>(rc) : make_float2(-INFINITY, 0.0f);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            v[x][i][k] = on ? *reinterpret_cast<const float2*>(rc + 2 + kh * 256 + 64 * k + 2 * lane)
+                                            : make_float2(0.0f, 0.0f);
+                        // pull the record's second half towards L2 while the first is reduced
+                        if (kh == 0 && on && lane < 8)
+                            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(rc + 2 + 256 + 32 * lane));
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < 2; x++) {
+                    const float Mn = fmaxf(fmaxf(M[x], ml[x][0].x), fmaxf(fmaxf(ml[x][1].x, ml[x][2].x), ml[x][3].x));
+                    if (Mn > -INFINITY) {
+                        const float s = exp2f(M[x] - Mn);
+                        L[x] *= s;
+#pragma unroll
+                        for (int k = 0; k < 8; k++) acc[x][k] *= s;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float w = exp2f(ml[x][i].x - Mn);
+                            L[x] = fmaf(w, ml[x][i].y, L[x]);
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                acc[x][2 * k] = fmaf(w, v[x][i][k].x, acc[x][2 * k]);
+                                acc[x][2 * k + 1] = fmaf(w, v[x][i][k].y, acc[x][2 * k + 1]);
+                            }
+                        }
+                        M[x] = Mn;
+                    }
+                    p[x] += 4;
+                }
+            }
+            MTR(3 + 4 * kh);
+            // the first half's MMAs read the operand buffers until they complete
+            if (kh == 1 && pr == 0) ok = mbar_wait(bar_mma, 0, fail_flag, status);
+            MTR(4 + 4 * kh);
+#pragma unroll
+            for (int x = 0; x < 2; x++) {
+                const float inv = L[x] > 0.0f ? 1.0f / L[x] : 0.0f;
+                const uint32_t rr = 4 * warp + 2 * pr + x;
+                const uint32_t off = rr * 128 + (((lane / 4) ^ (rr & 7)) << 4) + (lane % 4) * 4;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float o0 = acc[x][2 * k] * inv, o1 = acc[x][2 * k + 1] * inv;
+                    const T h0 = Elem<T>::from_f32(o0), h1 = Elem<T>::from_f32(o1);
+                    *reinterpret_cast<uint32_t*>(sm + OFF_AHI + k * A_SUB + off) = Elem<T>::pack2(o0, o1);
+                    *reinterpret_cast<uint32_t*>(sm + OFF_ALO + k * A_SUB + off) =
+                        Elem<T>::pack2(o0 - Elem<T>::to_f32(h0), o1 - Elem<T>::to_f32(h1));
+                }
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        tc_fence_before();
+        __syncthreads();
+        MTR(5 + 4 * kh);
+        if (warp == 0) {
+            if (kh == 0) ok = mbar_wait(bar_w, 0, fail_flag, status) && ok;
+            tc_fence_after();
+            if (ok && elect_one()) {
+#pragma unroll
+                for (int s = 0; s < 4; s++) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint32_t b = desc_lo(sW + (kh * 4 + s) * W_SUB + k * 32);
+                        tc_mma(tmem, desc_lo(sAhi + s * A_SUB + k * 32), DESC_HI, b, DESC_HI, IDESC,
+                               (kh == 0 && s == 0 && k == 0) ? 0u : 1u);
+                        tc_mma(tmem, desc_lo(sAlo + s * A_SUB + k * 32), DESC_HI, b, DESC_HI, IDESC, 1u);
+                    }
+                }
+                tc_commit(bar_mma);
+            }
+            __syncwarp();
+        }
+        MTR(6 + 4 * kh);
+    }
+
+    if (warp < 4) {
+        // D (M=64): rows 16*warp .. 16*warp+15 sit in lanes 0-15 of the warp's TMEM sub-partition
+        ok = mbar_wait(bar_mma, 1, fail_flag, status) && ok;
+        ok = __all_sync(0xffffffffu, ok);
+        MTR(11);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t row = r0 + 16 * warp + lane;
+#pragma unroll 1
+            for (int c = 0; c < kVDim / 32; c++) {
+                uint32_t o[32];
+                tc_ld32(tmem + ((warp * 32u) << 16) + c * 32, o);
+                tc_wait_ld();
+                if (lane < 16 && row < rows) {
+                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t(row) * H + h) * kVDim + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            pk[i] = Elem<T>::pack2(__uint_as_float(o[8 * q + 2 * i]), __uint_as_float(o[8 * q + 2 * i + 1]));
+                        dst[q] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+#ifdef MLA_TC5_TRACE
+    if (tid == 0 && blockIdx.x == 5) {
+        const long long e = clock64();
+        printf("[merge] prologue %lld phase1 %lld | h0: reduce %lld wait %lld write+sync %lld issue %lld | h1: reduce %lld wait %lld write+sync %lld issue %lld | mma wait %lld epilogue %lld\n",
+               mtr[1] - mtr[0], mtr[2] - mtr[1], mtr[3] - mtr[2], mtr[4] - mtr[3], mtr[5] - mtr[4], mtr[6] - mtr[5], mtr[7] - mtr[6],
+               mtr[8] - mtr[7], mtr[9] - mtr[8], mtr[10] - mtr[9], mtr[11] - mtr[10], e - mtr[11]);
+    }
+#endif
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+int merge_tc5_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES);
+    return int(e);
+}
+
+// w_map: host CUtensorMap over this layer's W_UV ([H*128 outputs][512 dims], box 64 dims x 128 outputs, 128-byte swizzle)
+int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, const void* w_map,
+                     void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st)
+{
+    if (rows == 0) return 0;
+    const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
+    dim3 grid(H, (rows + MT - 1) / MT);
+    if (dtype == 0)
+        merge_outproj_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(*map, recs, row_seg_begin, n_parts,
+                                                                               static_cast<__half*>(out), rows, H, status);
+    else
+        merge_outproj_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
+            *map, recs, row_seg_begin, n_parts, static_cast<__nv_bfloat16*>(out), rows, H, status);
+    return int(cudaGetLastError());
+}
+
+}  // namespace mla
