@@ -1,0 +1,348 @@
+// q absorption (+ optionally the cache append of the same layer-step) on the 5th-generation tensor
+// cores, sm_100a.
+//
+//   q_abs[r][h][d] = sum_{i<128} q[r][h][i] * W_UK[h*128+i][d],  d < 512;  q_abs[r][h][512..575] = q_rope
+//   (reference: transformer.cpp:2563-2573; a query row gets the layout of a cache row)
+//
+// Absorb blocks: one per (head, group of 64 query rows).  W_UK_h^T ([512 d][128 i], contraction index
+// contiguous, made once at registration) arrives by TMA as two K-major sub-tiles [512 d][64 i]
+// (128 KB); the threads copy q_nope[64 rows][128] into swizzled operand rows; D[64 x 512] fills the
+// 512 TMEM columns with 16 tcgen05.mma M=64 N=256 K=16; 16 warps drain TMEM into whole 256-byte
+// row pieces of q_abs.
+//
+// Append blocks (present when the caller fuses the two steps): four new rows per block, the
+// bit-exact RMSNorm + RoPE + scatter of append_kernel (mla_kernels.cu), 128 threads per row.  They
+// share the launch because the append is a chain of dependent float additions that takes as long
+// as the absorb itself and needs only a handful of SMs.
+#include <cuda.h>
+
+#include "mla_launch.h"
+
+namespace mla {
+
+namespace {
+
+constexpr int MT = 64;                          // query rows per absorb block
+constexpr int W_SUB = kRank * 128;              // 65,536: [512 d][64 i]
+constexpr int W_BYTES = 2 * W_SUB;              // 131,072
+constexpr int A_SUB = MT * 128;                 // 8,192: [64 rows][64 i]
+constexpr int OFF_W = 0;
+constexpr int OFF_A = OFF_W + W_BYTES;
+constexpr int OFF_MISC = OFF_A + 2 * A_SUB;     // 147,456
+constexpr int M_BAR = 0;                        // [0] W landed, [1] MMAs complete
+constexpr int M_TMEM = 16;
+constexpr int M_FAIL = 20;
+constexpr int MISC_BYTES = 64;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // + slack to round the base up to 1 KB
+constexpr int NUM_THREADS = 512;
+constexpr int APPEND_ROWS = NUM_THREADS / 128;  // rows per append block
+constexpr uint32_t TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded: gives up after about two seconds, raises the status bit and tells the block through `fail_flag`
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* fail_flag, uint32_t* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*fail_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *fail_flag = 1;
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor halves (K-major, 128-byte swizzle, 8-row groups 1 KB apart)
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+struct AppendArgs {          // rows == 0: no append blocks in this launch
+    const void* kv_a;
+    void* pool;              // this layer's slice of the cache pool
+    uint64_t pool_slots;
+    const void* norm_w;
+    const float* cos_sin;
+    uint32_t cs_rows;
+    float eps;
+    const uint32_t* row_pos;
+    const uint64_t* row_slot;
+    uint32_t rows;
+};
+
+// One new cache row per 128 threads; every statement mirrors append_kernel (mla_kernels.cu), which
+// documents the reference's rounding sequence.  All threads of the block reach every barrier.
+template <typename T>
+__device__ __forceinline__ void append_rows(const AppendArgs& a, uint32_t first_row, uint32_t* status)
+{
+    __shared__ __align__(16) T xin[APPEND_ROWS][kRow];
+    __shared__ __align__(16) T xout[APPEND_ROWS][kRow];
+    __shared__ float sq[APPEND_ROWS][kRank];
+    __shared__ float rinv_s[APPEND_ROWS];
+    const uint32_t g = threadIdx.x / 128, tid = threadIdx.x % 128, r = first_row + g;
+    const T* kv_a = static_cast<const T*>(a.kv_a);
+    const T* norm_w = static_cast<const T*>(a.norm_w);
+    T* pool = static_cast<T*>(a.pool);
+    bool live = r < a.rows;
+    uint64_t slot = 0;
+    uint32_t pos = 0;
+    if (live) {
+        slot = a.row_slot[r];
+        pos = a.row_pos[r];
+        if (slot == ~uint64_t(0)) live = false;          // a query-only row: nothing to append
+        else if (slot >= a.pool_slots || pos >= a.cs_rows) {
+            if (tid == 0) atomicOr(status, ST_BAD_SLOT);
+            live = false;
+        }
+    }
+    constexpr int kChunks = kRow * 2 / 16;   // 72 x 16 bytes
+    if (live && tid < kChunks)
+        reinterpret_cast<uint4*>(xin[g])[tid] = reinterpret_cast<const uint4*>(kv_a + size_t(r) * kRow)[tid];
+    __syncthreads();
+    if (live) {
+        for (int i = tid; i < kRank; i += 128) {
+            const float v = Elem<T>::to_f32(xin[g][i]);
+            sq[g][i] = __fmul_rn(v, v);
+        }
+        if (tid >= 32 && tid < 64) {
+            const int i = tid - 32;
+            const float c = a.cos_sin[size_t(pos) * kRope + i];
+            const float s = a.cos_sin[size_t(pos) * kRope + 32 + i];
+            const float x0 = Elem<T>::to_f32(xin[g][kRank + i]);
+            const float x1 = Elem<T>::to_f32(xin[g][kRank + 32 + i]);
+            xout[g][kRank + i]      = Elem<T>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+            xout[g][kRank + 32 + i] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s)));
+        }
+    }
+    __syncthreads();
+    if (live && tid == 0) {
+        float ss = 0.0f;
+#pragma unroll 16
+        for (int i = 0; i < kRank; i++) ss = __fadd_rn(ss, sq[g][i]);
+        rinv_s[g] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(kRank)), a.eps)));
+    }
+    __syncthreads();
+    if (live) {
+        const float rinv = rinv_s[g];
+        for (int i = tid; i < kRank; i += 128) {
+            const float v = __fmul_rn(Elem<T>::to_f32(xin[g][i]), rinv);
+            xout[g][i] = Elem<T>::from_f32(__fmul_rn(v, Elem<T>::to_f32(norm_w[i])));
+        }
+    }
+    __syncthreads();
+    if (live && tid < kChunks)
+        reinterpret_cast<uint4*>(pool + slot * kRow)[tid] = reinterpret_cast<const uint4*>(xout[g])[tid];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict__ q, T* __restrict__ q_abs, uint32_t rows,
+                  uint32_t H, uint32_t absorb_blocks, const AppendArgs app, uint32_t* __restrict__ status)
+{
+    if (blockIdx.x >= absorb_blocks) {
+        append_rows<T>(app, (blockIdx.x - absorb_blocks) * APPEND_ROWS, status);
+        return;
+    }
+    extern __shared__ unsigned char absorb_tc5_smem[];
+    const uint32_t raw = smem_u32(absorb_tc5_smem);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* sm = absorb_tc5_smem + (base - raw);
+    const uint32_t sW = base + OFF_W, sA = base + OFF_A;
+    const uint32_t bar_w = base + OFF_MISC + M_BAR, bar_mma = bar_w + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
+    volatile int* fail_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_FAIL);
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t h = blockIdx.x % H, r0 = (blockIdx.x / H) * MT;
+
+    if (tid == 0) {
+        *fail_flag = 0;
+        mbar_init(bar_w, 1);
+        mbar_init(bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_expect_tx(bar_w, W_BYTES);                      // W_UK_h^T: four boxes of 64 i x 256 d
+#pragma unroll 1
+        for (int bx = 0; bx < 4; bx++)
+            tma_load_2d(sW + (bx / 2) * W_SUB + (bx % 2) * (W_SUB / 2), &map_w, bar_w, 64 * (bx / 2), int(h) * kRank + 256 * (bx % 2));
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    // q_nope tile -> two swizzled K-major sub-tiles; q_rope -> behind the absorbed dims
+    for (uint32_t c = tid; c < MT * 16; c += NUM_THREADS) {                 // 16 chunks of 16 bytes per row
+        const uint32_t rr = c / 16, ch = c % 16, r = r0 + rr;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim)[ch];
+        *reinterpret_cast<uint4*>(sm + OFF_A + (ch / 8) * A_SUB + rr * 128 + (((ch % 8) ^ (rr & 7)) << 4)) = v;
+    }
+    for (uint32_t c = tid; c < MT * 8; c += NUM_THREADS) {                  // rope: 8 chunks per row
+        const uint32_t rr = c / 8, ch = c % 8, r = r0 + rr;
+        if (r < rows)
+            reinterpret_cast<uint4*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[ch] =
+                reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim + kNope)[ch];
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0) {
+        ok = mbar_wait(bar_w, 0, fail_flag, status);
+        tc_fence_after();
+        if (ok && elect_one()) {
+            constexpr uint32_t IDESC = instr_desc(Fmt<T>::v, MT, 256);
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+#pragma unroll
+                for (int s = 0; s < 2; s++) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        tc_mma(tmem + half * 256, desc_lo(sA + s * A_SUB + k * 32), DESC_HI,
+                               desc_lo(sW + s * W_SUB + half * (W_SUB / 2) + k * 32), DESC_HI, IDESC, (s == 0 && k == 0) ? 0u : 1u);
+                }
+            }
+            tc_commit(bar_mma);
+        }
+        __syncwarp();
+    }
+    // D (M=64): rows 16*q .. 16*q+15 sit in lanes 0-15 of TMEM sub-partition q; warp w drains the
+    // 128 columns 128*(w/4) .. of sub-partition w%4
+    ok = mbar_wait(bar_mma, 0, fail_flag, status) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+        tc_fence_after();
+        const uint32_t qp = warp % 4, cg = warp / 4;
+        const uint32_t row = r0 + 16 * qp + lane;
+#pragma unroll 1
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[32];
+            tc_ld32(tmem + ((qp * 32u) << 16) + cg * 128 + c * 32, o);
+            tc_wait_ld();
+            if (lane < 16 && row < rows) {
+                uint4* dst = reinterpret_cast<uint4*>(q_abs + (size_t(row) * H + h) * kRow + cg * 128 + c * 32);
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        pk[i] = Elem<T>::pack2(__uint_as_float(o[8 * x + 2 * i]), __uint_as_float(o[8 * x + 2 * i + 1]));
+                    dst[x] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+int absorb_tc5_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(absorb_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(absorb_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    // every kernel of a layer-step asks for the same (maximal) shared-memory carve-out, so the SMs are not
+    // re-partitioned between consecutive launches
+    e = cudaFuncSetAttribute(absorb_tc5_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(absorb_tc5_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return int(e);
+}
+
+// w_map: host CUtensorMap over this layer's W_UK^T ([H*512 d][128 i], box 64 i x 256 d, 128-byte swizzle).
+// With kv_a != nullptr the launch also appends the step's new rows to the layer's cache pool.
+int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, uint32_t rows, uint32_t H, const void* kv_a,
+                      void* layer_pool, uint64_t pool_slots, const void* norm_w, const float* cos_sin, uint32_t cs_rows,
+                      float eps, const StepMeta& m, uint32_t* status, cudaStream_t st)
+{
+    if (rows == 0) return 0;
+    const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
+    AppendArgs app{};
+    if (kv_a) app = AppendArgs{kv_a, layer_pool, pool_slots, norm_w, cos_sin, cs_rows, eps, m.row_pos, m.row_slot, m.rows};
+    const uint32_t absorb_blocks = H * ((rows + MT - 1) / MT);
+    const uint32_t append_blocks = (app.rows + APPEND_ROWS - 1) / APPEND_ROWS;
+    // append blocks carry the trailing indices; for decode batches all blocks are resident at once (H + rows/4 <= SMs)
+    dim3 grid(absorb_blocks + append_blocks);
+    if (dtype == 0)
+        absorb_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(*map, static_cast<const __half*>(q), static_cast<__half*>(q_abs),
+                                                                        rows, H, absorb_blocks, app, status);
+    else
+        absorb_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
+            *map, static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app, status);
+    return int(cudaGetLastError());
+}
+
+}  // namespace mla

@@ -32,6 +32,8 @@ struct LayerW {
     bool set = false;
     // W_UV as ([H*128 outputs][512 dims]) with a box of 64 dims x 128 outputs, for the tcgen05 merge kernel
     alignas(64) CUtensorMap w_uv_map;
+    // W_UK^T as ([H*512 d][128 i]) with a box of 64 i x 256 d, for the tcgen05 absorb kernel
+    alignas(64) CUtensorMap w_uk_map;
     bool has_map = false;
 };
 
@@ -307,12 +309,23 @@ int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row
               float* exported, uint32_t rows, cudaStream_t st);
 
 // absorb -> split-KV attention -> merge (+ W_UV, or export of the merged partial state)
-int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st)
+// With fused_kv_a the absorb launch also appends the step's new rows (the caller then skips run_append).
+int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st,
+               const void* fused_kv_a = nullptr)
 {
     const mla::StepMeta& m = c->meta;
     if (m.rows == 0) return MLA_OK;
     const uint32_t H = c->cfg.n_heads;
-    mla::launch_absorb(int(c->cfg.dtype), q, c->layers[layer].w_uk, c->q_abs, m.rows, H, st);
+    const LayerW& lw = c->layers[layer];
+    if (lw.has_map) {
+        const int ae = mla::launch_absorb_tc5(int(c->cfg.dtype), q, &lw.w_uk_map, c->q_abs, m.rows, H, fused_kv_a,
+                                              layer_pool(c, layer), c->pool_slots, lw.norm, c->cos_sin, c->cs_rows,
+                                              c->cfg.rms_norm_eps, m, c->status_dev, st);
+        if (ae != 0) return fail(c, MLA_ERR_CUDA, std::string("absorb launch: ") + cudaGetErrorString(cudaError_t(ae)));
+    } else {
+        if (fused_kv_a) return fail(c, MLA_ERR_STATE, "fused append needs the layer's tensor maps");
+        mla::launch_absorb(int(c->cfg.dtype), q, lw.w_uk, c->q_abs, m.rows, H, st);
+    }
     int e;
     const bool timed = c->profiling && c->prof_used < c->prof_events.size();
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
@@ -332,6 +345,14 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     c->launches += 3;
     CU_TRY(c, cudaGetLastError());
     return MLA_OK;
+}
+
+// one layer of a step: append + attention, with the append riding in the absorb launch where it can
+int run_layer(mla_ctx* c, uint32_t layer, const void* kv_a, const void* q, void* out, cudaStream_t st)
+{
+    if (c->layers[layer].has_map) return run_attend(c, layer, q, out, nullptr, st, kv_a);
+    if (int e = run_append(c, layer, kv_a, st)) return e;
+    return run_attend(c, layer, q, out, nullptr, st);
 }
 
 using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -365,6 +386,14 @@ int make_weight_map(mla_ctx* c, uint32_t layer)
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(W_UV) failed with code " + std::to_string(int(r)));
+    const cuuint64_t kdims[2] = {cuuint64_t(mla::kNope), cuuint64_t(c->cfg.n_heads) * mla::kRank};
+    const cuuint64_t kstrides[1] = {cuuint64_t(mla::kNope) * 2};
+    const cuuint32_t kbox[2] = {64, 256};
+    const CUresult r2 = enc(&lw.w_uk_map, dt, 2, lw.w_uk, kdims, kstrides, kbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r2 != CUDA_SUCCESS)
+        return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(W_UK) failed with code " + std::to_string(int(r2)));
     lw.has_map = true;
     return MLA_OK;
 }
@@ -563,6 +592,10 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
             cp->err = std::string("tcgen05 pair kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
             return bail(MLA_ERR_CUDA);
         }
+    }
+    if (int ce = mla::absorb_tc5_configure()) {
+        cp->err = std::string("tcgen05 absorb kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
     }
     if (int ce = mla::merge_tc5_configure()) {
         cp->err = std::string("tcgen05 merge kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
@@ -806,9 +839,7 @@ int mla_step_layers(mla_ctx* c, uint32_t layer_begin, uint32_t n_layers, const v
     for (uint32_t i = 0; i < n_layers; i++) {
         const uint32_t layer = layer_begin + i;
         if (int e = check_layer(c, layer, true)) return e;
-        if (int e = run_append(c, layer, static_cast<const char*>(kv_a) + i * kv_b, st)) return e;
-        if (int e = run_attend(c, layer, static_cast<const char*>(q) + i * q_b, static_cast<char*>(out) + i * o_b,
-                               nullptr, st))
+        if (int e = run_layer(c, layer, static_cast<const char*>(kv_a) + i * kv_b, static_cast<const char*>(q) + i * q_b, static_cast<char*>(out) + i * o_b, st))
             return e;
     }
     return MLA_OK;
@@ -870,8 +901,7 @@ int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const
         // (or calls mla_status) before reading out_host
         CU_TRY(c, cudaMemcpyAsync(d_kv, kv_a_host, kv_b, cudaMemcpyHostToDevice, st));
         CU_TRY(c, cudaMemcpyAsync(d_q, q_host, q_b, cudaMemcpyHostToDevice, st));
-        if (int e = run_append(c, layer, d_kv, st)) return e;
-        if (int e = run_attend(c, layer, d_q, d_out, nullptr, st)) return e;
+        if (int e = run_layer(c, layer, d_kv, d_q, d_out, st)) return e;
         CU_TRY(c, cudaMemcpyAsync(out_host, d_out, o_b, cudaMemcpyDeviceToHost, st));
         return MLA_OK;
     }
@@ -885,8 +915,7 @@ int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const
     std::memcpy(static_cast<char*>(c->h_in) + kv_cap, q_host, q_b);
     CU_TRY(c, cudaMemcpyAsync(d_kv, c->h_in, kv_b, cudaMemcpyHostToDevice, st));
     CU_TRY(c, cudaMemcpyAsync(d_q, static_cast<char*>(c->h_in) + kv_cap, q_b, cudaMemcpyHostToDevice, st));
-    if (int e = run_append(c, layer, d_kv, st)) return e;
-    if (int e = run_attend(c, layer, d_q, d_out, nullptr, st)) return e;
+    if (int e = run_layer(c, layer, d_kv, d_q, d_out, st)) return e;
     CU_TRY(c, cudaMemcpyAsync(c->h_out, d_out, o_b, cudaMemcpyDeviceToHost, st));
     CU_TRY(c, cudaStreamSynchronize(st));
     std::memcpy(out_host, c->h_out, o_b);

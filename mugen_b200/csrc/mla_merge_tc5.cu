@@ -350,6 +350,12 @@ int merge_tc5_configure()
     if (e != cudaSuccess) return int(e);
     e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    // every kernel of a layer-step asks for the same (maximal) shared-memory carve-out, so the SMs are not
+    // re-partitioned between consecutive launches
+    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     return int(e);
 }
 
