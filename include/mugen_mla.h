@@ -189,13 +189,16 @@ int mla_merge_partials(mla_ctx* ctx, uint32_t layer, uint32_t n_parts, uint32_t 
 /* ---- introspection used by benchmarks --------------------------------------------------- */
 /* Kernel launches issued by this context since creation. */
 int mla_launch_count(const mla_ctx* ctx, uint64_t* n);
-/* Device timing of the split-KV attention kernel alone: while enabled, every launch of that
- * kernel is bracketed by CUDA events on the launching stream (up to 8192 launches are kept).
+/* Device timing of the split-KV attention kernel alone: while enabled, launches of that kernel
+ * are bracketed by CUDA events on the launching stream (up to 8192 launches are kept).  on = 1
+ * brackets every launch, on = N > 1 every N-th one: an event between two kernels keeps the second
+ * from becoming resident while the first drains (the kernels of a step are launched as programmatic
+ * dependents), so a sparse sample disturbs the step it measures less.
  * mla_profile_read synchronises those events and returns launches and their summed duration,
  * then clears the record. */
 int mla_profile_enable(mla_ctx* ctx, int on);
 int mla_profile_read(mla_ctx* ctx, uint32_t* launches, float* total_ms);
-/* Name of the attention kernel family in use ("mma" or "tcgen05"). */
+/* Name of the attention kernel family in use ("mma", "tcgen05", "tcgen05-pair", "tcgen05-pair128"). */
 const char* mla_kernel_name(const mla_ctx* ctx);
 /* Reads `n` latent rows [row_begin, row_begin+n) of (layer, seq) back to HOST memory. */
 int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,

@@ -202,7 +202,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict__ q, T* __restrict__ q_abs, uint32_t rows,
                   uint32_t H, uint32_t absorb_blocks, const AppendArgs app, uint32_t* __restrict__ status)
 {
+    grid_launch_dependents();
     if (blockIdx.x >= absorb_blocks) {
+        grid_dependency_wait();
         append_rows<T>(app, (blockIdx.x - absorb_blocks) * APPEND_ROWS, status);
         return;
     }
@@ -233,6 +235,8 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
+    // the weights are constant; everything below reads or writes what earlier kernels of the stream touch
+    grid_dependency_wait();
     // q_nope tile -> two swizzled K-major sub-tiles; q_rope -> behind the absorbed dims
     for (uint32_t c = tid; c < MT * 16; c += NUM_THREADS) {                 // 16 chunks of 16 bytes per row
         const uint32_t rr = c / 16, ch = c % 16, r = r0 + rr;
@@ -337,12 +341,10 @@ int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, 
     // append blocks carry the trailing indices; for decode batches all blocks are resident at once (H + rows/4 <= SMs)
     dim3 grid(absorb_blocks + append_blocks);
     if (dtype == 0)
-        absorb_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(*map, static_cast<const __half*>(q), static_cast<__half*>(q_abs),
-                                                                        rows, H, absorb_blocks, app, status);
-    else
-        absorb_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
-            *map, static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app, status);
-    return int(cudaGetLastError());
+        return int(launch_pdl(absorb_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, static_cast<const __half*>(q),
+                              static_cast<__half*>(q_abs), rows, H, absorb_blocks, app, status));
+    return int(launch_pdl(absorb_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map,
+                          static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app, status));
 }
 
 }  // namespace mla

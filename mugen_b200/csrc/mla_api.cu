@@ -81,6 +81,7 @@ struct mla_ctx {
 
     // optional per-launch timing of the attention kernel
     bool profiling = false;
+    uint32_t prof_stride = 1, prof_seq = 0;     // every prof_stride-th attention launch is timed
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
     size_t prof_used = 0;
 
@@ -327,7 +328,7 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
         mla::launch_absorb(int(c->cfg.dtype), q, lw.w_uk, c->q_abs, m.rows, H, st);
     }
     int e;
-    const bool timed = c->profiling && c->prof_used < c->prof_events.size();
+    const bool timed = c->profiling && c->prof_used < c->prof_events.size() && (c->prof_seq++ % c->prof_stride) == 0;
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
         e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
@@ -958,6 +959,8 @@ int mla_profile_enable(mla_ctx* c, int on)
         }
     }
     c->profiling = on != 0;
+    c->prof_stride = on > 1 ? uint32_t(on) : 1;
+    c->prof_seq = 0;
     return MLA_OK;
 }
 

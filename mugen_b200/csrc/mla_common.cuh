@@ -26,6 +26,31 @@ enum : uint32_t {
     ST_BAD_ALIGNMENT = 1u << 4,   // dynamic shared memory did not start on the 1 KB boundary a kernel relies on
 };
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may become resident while the
+// previous kernel of the stream is still draining.  It must call grid_dependency_wait() before its
+// first access to memory that any earlier kernel of the stream reads or writes (the wait returns
+// once the previous grid has completed and flushed; completion is transitive because every kernel
+// of the chain waits before it completes).  grid_launch_dependents() lets the next kernel's blocks
+// start as soon as this kernel's blocks have all begun.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename K, typename... Args>
+inline cudaError_t launch_pdl(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename T> struct Elem;
 template <> struct Elem<__half> {
     using pair = __half2;

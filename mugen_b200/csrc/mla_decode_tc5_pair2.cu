@@ -336,6 +336,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         return;
     }
 
+    grid_launch_dependents();
     if (tid == 0) {
         *abort_flag = 0;
         need_flag[0] = need_flag[1] = 0;
@@ -372,6 +373,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    grid_dependency_wait();          // queries, new cache rows and the state records belong to earlier kernels until here
 
     // Page of super-tile j that block `r` stages as K (and whose tokens are columns 64r .. 64r+63 of
     // the score tile).  A segment with an odd page count repeats its last page in the second half:
@@ -872,12 +874,10 @@ int launch_decode_tc5_pair128(int dtype, const void* tmaps, uint32_t layer, uint
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
-        decode_tc5_pair128_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[4], maps[5], maps[6], layer, n_pages,
-                                                                                m, recs, H, scale_log2, status);
-    else
-        decode_tc5_pair128_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[4], maps[5], maps[6], layer,
-                                                                                       n_pages, m, recs, H, scale_log2, status);
-    return int(cudaGetLastError());
+        return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4], maps[5],
+                              maps[6], layer, n_pages, m, recs, H, scale_log2, status));
+    return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4],
+                          maps[5], maps[6], layer, n_pages, m, recs, H, scale_log2, status));
 }
 
 }  // namespace mla

@@ -155,6 +155,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     long long mtr[12] = {0};
 #endif
     MTR(0);
+    grid_launch_dependents();
     if (tid == 0) {
         *fail_flag = 0;
         mbar_init(bar_w, 1);
@@ -187,6 +188,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     // sweep and a row with up to four parts costs a single round trip to memory.
     constexpr uint32_t IDESC = instr_desc(Fmt<T>::v, MT, kVDim);
     bool ok = true;
+    grid_dependency_wait();          // W_UV is constant and already on its way; the partial states are not
     uint32_t pb4[4], pe4[4];                              // part ranges of this warp's four rows
 #pragma unroll
     for (int x = 0; x < 4; x++) {
@@ -367,12 +369,10 @@ int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
     dim3 grid(H, (rows + MT - 1) / MT);
     if (dtype == 0)
-        merge_outproj_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(*map, recs, row_seg_begin, n_parts,
-                                                                               static_cast<__half*>(out), rows, H, status);
-    else
-        merge_outproj_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
-            *map, recs, row_seg_begin, n_parts, static_cast<__nv_bfloat16*>(out), rows, H, status);
-    return int(cudaGetLastError());
+        return int(launch_pdl(merge_outproj_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin,
+                              n_parts, static_cast<__half*>(out), rows, H, status));
+    return int(launch_pdl(merge_outproj_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs,
+                          row_seg_begin, n_parts, static_cast<__nv_bfloat16*>(out), rows, H, status));
 }
 
 }  // namespace mla

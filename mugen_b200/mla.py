@@ -183,7 +183,8 @@ class MlaContext:
         self._check(self.lib.mla_launch_count(self.h, C.byref(v)))
         return v.value
 
-    def profile_enable(self, on: bool) -> None:
+    def profile_enable(self, on) -> None:
+        """False/0: off; True/1: time every attention launch; N > 1: every N-th launch."""
         self._check(self.lib.mla_profile_enable(self.h, int(on)))
 
     def profile_read(self) -> tuple[int, float]:
