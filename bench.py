@@ -4,8 +4,9 @@
 Workload (BASELINE.json configs[2], the one the headline target is quoted on): DeepSeek-V3-shaped
 MLA decode — 61 layers, 128 heads, batch 64, context 16384 per sequence, bf16 paged latent cache
 (64-token pages, shuffled block tables), one token appended per sequence per step.  One "step" is
-one decode step of the whole attention stack: for every layer append(new c_kv/k_rope rows) then
-absorbed attention (q absorb -> split-KV attention -> merge -> W_UV).  Inputs are seeded synthetic
+one decode step of the whole attention stack: for every layer append(new c_kv/k_rope rows) and
+absorbed attention (q absorb -> split-KV attention -> merge -> W_UV), three kernel launches per layer
+through mla_step_layers (the append runs in spare blocks of the absorb launch).  Inputs are seeded synthetic
 tensors of the model's shapes; with N GPUs the batch of 64 is sharded by sequence (no collective on
 the data path), so total work is fixed ("strong" scaling).
 

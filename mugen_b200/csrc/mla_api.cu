@@ -65,8 +65,10 @@ struct mla_ctx {
     uint32_t max_segs = 0;
     uint32_t workers = 1;
     uint32_t* status_dev = nullptr;
-    alignas(64) CUtensorMap tmaps[7];   // + [3..6]: whole-row views (all 9 sub-tiles of a row range in ONE box), see make_tensor_maps
-    // legacy comment follows:   // tcgen05 paths: [0] cache pool (64-token box), [1] absorbed queries, [2] cache pool (32-token box)
+    // tensor maps of the tcgen05 attention kernels (make_tensor_maps): [0] cache pool, box 64 values x 64 tokens;
+    // [1] absorbed queries; [2] cache pool, 32-token box; [3..6] whole-row views of pool and queries (all sub-tiles
+    // of a row range in ONE box)
+    alignas(64) CUtensorMap tmaps[7];
 
     // metadata upload ring
     MetaBuf ring[kMetaRing];
@@ -203,7 +205,8 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     std::vector<Segment> segs;
     std::vector<uint32_t> row_seg_begin, cta_seg_begin;
     if (with_segments) {
-        mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin);
+        mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin,
+                                  c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? 2u : 1u);
         if (segs.size() > c->max_segs)
             return fail(c, MLA_ERR_CAPACITY, "step needs " + std::to_string(segs.size()) +
                                                  " KV segments, workspace holds " + std::to_string(c->max_segs));

@@ -175,11 +175,22 @@ struct Segment {
     uint32_t page_end;
 };
 
+// granule_pages > 1: the attention kernel walks a segment in tiles of that many pages, so shares are
+// counted and cut in tiles (a cut inside a tile would leave two half-empty tiles that cost full ones).
 inline void plan_balanced(const std::vector<uint32_t>& attend_lens, uint32_t page_tokens,
                           uint32_t workers, std::vector<Segment>& segs,
                           std::vector<uint32_t>& row_seg_begin,
-                          std::vector<uint32_t>& worker_seg_begin)
+                          std::vector<uint32_t>& worker_seg_begin, uint32_t granule_pages = 1)
 {
+    if (granule_pages > 1) {
+        plan_balanced(attend_lens, page_tokens * granule_pages, workers, segs, row_seg_begin, worker_seg_begin, 1);
+        for (Segment& sg : segs) {
+            const uint32_t pages = (attend_lens[sg.row] + page_tokens - 1) / page_tokens;
+            sg.page_begin = std::min(pages, sg.page_begin * granule_pages);
+            sg.page_end = std::min(pages, sg.page_end * granule_pages);
+        }
+        return;
+    }
     const uint32_t rows = uint32_t(attend_lens.size());
     segs.clear();
     row_seg_begin.assign(rows + 1, 0);

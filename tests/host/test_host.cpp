@@ -98,6 +98,30 @@ static void test_planner()
     lens = {131072};
     plan_balanced(lens, 64, 148, segs, rsb, wsb);
     CHECK(segs.size() == 148 && rsb[1] == 148);
+    // two-page tiles: every cut inside a row falls on an even page, pages are still covered once, shares are
+    // equal in tiles; a row with an odd page count keeps its last single page
+    lens.assign(64, 16385);                                   // 257 pages = 129 tiles per row
+    plan_balanced(lens, 64, 74, segs, rsb, wsb, 2);
+    for (uint32_t r = 0; r < 64; r++) {
+        uint32_t next = 0;
+        for (uint32_t g = rsb[r]; g < rsb[r + 1]; g++) {
+            CHECK(segs[g].row == r && segs[g].page_begin == next && segs[g].page_end > next);
+            CHECK(segs[g].page_begin % 2 == 0);
+            CHECK(segs[g].page_end % 2 == 0 || segs[g].page_end == 257);
+            next = segs[g].page_end;
+        }
+        CHECK(next == 257);
+    }
+    for (uint32_t w = 0; w < 74; w++) {
+        uint64_t tiles = 0;
+        for (uint32_t g = wsb[w]; g < wsb[w + 1]; g++) tiles += (segs[g].page_end - segs[g].page_begin + 1) / 2;
+        CHECK(tiles == 111 || tiles == 112);
+    }
+    lens = {0, 1, 64, 65, 0, 1000, 0};
+    plan_balanced(lens, 64, 148, segs, rsb, wsb, 2);
+    total = 0;
+    for (auto& g : segs) total += g.page_end - g.page_begin;
+    CHECK(total == 0 + 1 + 1 + 2 + 0 + 16 + 0);
     // nothing at all
     lens.clear();
     plan_balanced(lens, 64, 148, segs, rsb, wsb);
