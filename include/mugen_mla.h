@@ -186,6 +186,14 @@ int mla_step_attend_partial(mla_ctx* ctx, uint32_t layer, const void* q, float* 
 int mla_merge_partials(mla_ctx* ctx, uint32_t layer, uint32_t n_parts, uint32_t rows,
                        const float* partials, void* out, void* stream);
 
+/* q-side RoPE (reference: step E of the decode driver, transformer.cpp:3882-3921, a CPU loop between two GPU
+ * round trips).  in_kernel = 1: q is passed as the W_q projection left it and the absorb kernel rotates the last
+ * 64 dims of every head with the row's position (NeoX pairs, YaRN frequencies, the same table and rounding as the
+ * k_rope rotation of the append; bit-exact against the reference loop).  in_kernel = 0 (default): q arrives
+ * rotated, which is cpu_mla_attention's own contract.  Rows of a step take the position of their new token,
+ * mla_attend_rows rows the last attended position; steps with query-only rows (n_new = 0) are refused while on. */
+int mla_set_q_rope(mla_ctx* ctx, int in_kernel);
+
 /* ---- introspection used by benchmarks --------------------------------------------------- */
 /* Kernel launches issued by this context since creation. */
 int mla_launch_count(const mla_ctx* ctx, uint64_t* n);

@@ -200,7 +200,8 @@ __device__ __forceinline__ void append_rows(const AppendArgs& a, uint32_t first_
 template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict__ q, T* __restrict__ q_abs, uint32_t rows,
-                  uint32_t H, uint32_t absorb_blocks, const AppendArgs app, uint32_t* __restrict__ status)
+                  uint32_t H, uint32_t absorb_blocks, const AppendArgs app, const float* __restrict__ q_cos_sin,
+                  const uint32_t* __restrict__ q_pos, uint32_t cs_rows, uint32_t* __restrict__ status)
 {
     grid_launch_dependents();
     if (blockIdx.x >= absorb_blocks) {
@@ -244,11 +245,31 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
         if (r < rows) v = reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim)[ch];
         *reinterpret_cast<uint4*>(sm + OFF_A + (ch / 8) * A_SUB + rr * 128 + (((ch % 8) ^ (rr & 7)) << 4)) = v;
     }
-    for (uint32_t c = tid; c < MT * 8; c += NUM_THREADS) {                  // rope: 8 chunks per row
-        const uint32_t rr = c / 8, ch = c % 8, r = r0 + rr;
-        if (r < rows)
-            reinterpret_cast<uint4*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[ch] =
-                reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim + kNope)[ch];
+    if (q_cos_sin == nullptr) {
+        for (uint32_t c = tid; c < MT * 8; c += NUM_THREADS) {              // rope part, already rotated: 8 chunks per row
+            const uint32_t rr = c / 8, ch = c % 8, r = r0 + rr;
+            if (r < rows)
+                reinterpret_cast<uint4*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[ch] =
+                    reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim + kNope)[ch];
+        }
+    } else {
+        // q-side RoPE (reference: transformer.cpp:3882-3921, NeoX pairs (i, i+32), YaRN frequencies): the same
+        // table and the same separately rounded products as the k_rope rotation of the append
+        for (uint32_t c = tid; c < MT * (kRope / 2); c += NUM_THREADS) {
+            const uint32_t rr = c / (kRope / 2), i = c % (kRope / 2), r = r0 + rr;
+            if (r >= rows) continue;
+            const uint32_t pos = q_pos[r];
+            if (pos >= cs_rows) {
+                if (i == 0) atomicOr(status, ST_BAD_SLOT);
+                continue;
+            }
+            const T* src = q + (size_t(r) * H + h) * kQDim + kNope;
+            T* dst = q_abs + (size_t(r) * H + h) * kRow + kRank;
+            const float cs = q_cos_sin[size_t(pos) * kRope + i], sn = q_cos_sin[size_t(pos) * kRope + 32 + i];
+            const float x0 = Elem<T>::to_f32(src[i]), x1 = Elem<T>::to_f32(src[32 + i]);
+            dst[i]      = Elem<T>::from_f32(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+            dst[32 + i] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(x0, sn)));
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     tc_fence_before();
@@ -327,10 +348,11 @@ int absorb_tc5_configure()
 }
 
 // w_map: host CUtensorMap over this layer's W_UK^T ([H*512 d][128 i], box 64 i x 256 d, 128-byte swizzle).
-// With kv_a != nullptr the launch also appends the step's new rows to the layer's cache pool.
+// With kv_a != nullptr the launch also appends the step's new rows to the layer's cache pool.  With rotate_q the
+// last 64 dims of every query head are rotated with the row's position (m.row_pos) before they are stored.
 int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, uint32_t rows, uint32_t H, const void* kv_a,
                       void* layer_pool, uint64_t pool_slots, const void* norm_w, const float* cos_sin, uint32_t cs_rows,
-                      float eps, const StepMeta& m, uint32_t* status, cudaStream_t st)
+                      float eps, const StepMeta& m, bool rotate_q, uint32_t* status, cudaStream_t st)
 {
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
@@ -342,9 +364,10 @@ int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, 
     dim3 grid(absorb_blocks + append_blocks);
     if (dtype == 0)
         return int(launch_pdl(absorb_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, static_cast<const __half*>(q),
-                              static_cast<__half*>(q_abs), rows, H, absorb_blocks, app, status));
+                              static_cast<__half*>(q_abs), rows, H, absorb_blocks, app, rotate_q ? cos_sin : nullptr, m.row_pos, cs_rows, status));
     return int(launch_pdl(absorb_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map,
-                          static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app, status));
+                          static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app,
+                          rotate_q ? cos_sin : nullptr, m.row_pos, cs_rows, status));
 }
 
 }  // namespace mla

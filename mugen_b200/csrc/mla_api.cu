@@ -82,6 +82,7 @@ struct mla_ctx {
     std::vector<uint32_t> step_seqs, step_nnew;
 
     // optional per-launch timing of the attention kernel
+    bool q_rope_in_kernel = false;  // queries arrive before their RoPE (mla_set_q_rope)
     bool profiling = false;
     uint32_t prof_stride = 1, prof_seq = 0;     // every prof_stride-th attention launch is timed
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
@@ -324,10 +325,11 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     if (lw.has_map) {
         const int ae = mla::launch_absorb_tc5(int(c->cfg.dtype), q, &lw.w_uk_map, c->q_abs, m.rows, H, fused_kv_a,
                                               layer_pool(c, layer), c->pool_slots, lw.norm, c->cos_sin, c->cs_rows,
-                                              c->cfg.rms_norm_eps, m, c->status_dev, st);
+                                              c->cfg.rms_norm_eps, m, c->q_rope_in_kernel, c->status_dev, st);
         if (ae != 0) return fail(c, MLA_ERR_CUDA, std::string("absorb launch: ") + cudaGetErrorString(cudaError_t(ae)));
     } else {
         if (fused_kv_a) return fail(c, MLA_ERR_STATE, "fused append needs the layer's tensor maps");
+        if (c->q_rope_in_kernel) return fail(c, MLA_ERR_UNSUPPORTED, "in-kernel q RoPE needs the layer's tensor maps");
         mla::launch_absorb(int(c->cfg.dtype), q, lw.w_uk, c->q_abs, m.rows, H, st);
     }
     int e;
@@ -759,6 +761,7 @@ int mla_attend_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_
     auto st = static_cast<cudaStream_t>(stream);
     std::vector<uint32_t> seqs;
     std::vector<RowSpec> rows(n);
+    uint32_t max_pos = 0;
     for (uint32_t r = 0; r < n; r++) {
         const auto* s = c->pt->seq(seq_ids[r]);
         if (!s) return fail(c, MLA_ERR_INVALID, "unknown sequence id " + std::to_string(seq_ids[r]));
@@ -768,8 +771,12 @@ int mla_attend_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_
         uint32_t idx = 0;
         for (; idx < seqs.size(); idx++) if (seqs[idx] == seq_ids[r]) break;
         if (idx == seqs.size()) seqs.push_back(seq_ids[r]);
-        rows[r] = {idx, attend_lens[r], 0, 0};
+        // the query stands at the last attended position (matters only when the library rotates q)
+        const uint32_t qpos = s->base_pos + (attend_lens[r] ? attend_lens[r] - 1 : 0);
+        rows[r] = {idx, attend_lens[r], qpos, 0};
+        max_pos = std::max(max_pos, qpos);
     }
+    if (n && c->q_rope_in_kernel) if (int e = ensure_rope_rows(c, max_pos + 1, st)) return e;
     if (int e = upload_meta(c, seqs, rows, true, st)) return e;
     return run_attend(c, layer, q, out, nullptr, st);
 }
@@ -802,7 +809,12 @@ int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const ui
     rows.reserve(total);
     for (uint32_t i = 0; i < n_seq; i++) {
         const auto* s = c->pt->seq(seqs[i]);
-        if (nn[i] == 0) rows.push_back({i, s->len, 0, ~uint64_t(0)});   // query-only row
+        if (nn[i] == 0) {                                              // query-only row
+            if (c->q_rope_in_kernel)
+                return fail(c, MLA_ERR_UNSUPPORTED, "a query-only row has no position of its own: rotate q on the caller's side "
+                                                    "(mla_set_q_rope(ctx, 0)) for KV-range shards that do not own the tail");
+            rows.push_back({i, s->len, 0, ~uint64_t(0)});
+        }
         for (uint32_t t = 0; t < nn[i]; t++) {
             const uint32_t local = s->len + t;
             rows.push_back({i, local + 1, s->base_pos + local, c->pt->slot(seqs[i], local)});
@@ -948,6 +960,14 @@ int mla_launch_count(const mla_ctx* c, uint64_t* n)
 {
     if (!c || !n) return MLA_ERR_INVALID;
     *n = c->launches;
+    return MLA_OK;
+}
+
+int mla_set_q_rope(mla_ctx* c, int in_kernel)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (c->in_step) return fail(c, MLA_ERR_STATE, "mla_set_q_rope inside step_begin/step_end");
+    c->q_rope_in_kernel = in_kernel != 0;
     return MLA_OK;
 }
 

@@ -46,10 +46,11 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
 
 // Absorb on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the layer's W_UK^T,
 // [H*512 d][128 i], box 64 i x 256 d, 128-byte swizzle.  With kv_a != nullptr the same launch appends the step's
-// new rows (launch_append's arguments) in extra blocks.
+// new rows (launch_append's arguments) in extra blocks.  rotate_q: q arrives before its RoPE; the kernel rotates
+// the last 64 dims of every head with the row's position (m.row_pos) and the cos/sin table.
 int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, uint32_t rows, uint32_t H, const void* kv_a,
                       void* layer_pool, uint64_t pool_slots, const void* norm_w, const float* cos_sin, uint32_t cs_rows,
-                      float eps, const StepMeta& m, uint32_t* status, cudaStream_t st);
+                      float eps, const StepMeta& m, bool rotate_q, uint32_t* status, cudaStream_t st);
 int absorb_tc5_configure();
 
 // The same merge + projection on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the

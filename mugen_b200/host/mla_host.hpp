@@ -150,6 +150,10 @@ public:
                                        out, stream));
     }
 
+    // Step E of the reference's decode driver (transformer.cpp:3882-3921) inside the absorb kernel: q is then
+    // passed as the W_q projection left it.  Off by default (cpu_mla_attention takes rotated queries).
+    auto set_q_rope_in_kernel(bool on) -> Status { return c_.wrap(mla_set_q_rope(c_.h_, on ? 1 : 0)); }
+
     // Decode-step scheduler: begin -> per layer (append, attend) -> end.
     auto step_begin(std::span<const uint32_t> seq_ids, std::span<const uint32_t> n_new = {}, void* stream = nullptr)
         -> Status

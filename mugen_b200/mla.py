@@ -183,6 +183,10 @@ class MlaContext:
         self._check(self.lib.mla_launch_count(self.h, C.byref(v)))
         return v.value
 
+    def set_q_rope(self, in_kernel: bool) -> None:
+        """True: q is passed before its RoPE and the absorb kernel rotates it with the row's position."""
+        self._check(self.lib.mla_set_q_rope(self.h, int(in_kernel)))
+
     def profile_enable(self, on) -> None:
         """False/0: off; True/1: time every attention launch; N > 1: every N-th launch."""
         self._check(self.lib.mla_profile_enable(self.h, int(on)))

@@ -298,6 +298,56 @@ def test_step_layers_equals_per_layer_calls(torch, kernel):
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(rows[0], rows[1])
 
 
+@pytest.mark.parametrize("dt", [synth.DT_F16, synth.DT_BF16])
+def test_q_rope_inside_the_absorb_kernel(torch, oracle, dt):
+    """Step E of the reference's decode driver (transformer.cpp:3882-3921) folded into the absorb
+    kernel: queries passed before their RoPE give bit-identical outputs to queries the checker
+    rotated at the same positions, for decode rows, a prefill chunk (one position per row) and the
+    explicit-length call; and they agree with the CPU attention over the rotated queries."""
+    H, lens, chunk = 64, [130, 64], 5
+    case = synth.make_layer_case(777, H, [n + chunk for n in lens], dt)
+    rng = np.random.default_rng(12)
+    n_new = [1, chunk]
+    R = sum(n_new)
+    kv = synth.to_bits(rng.standard_normal((R, 576), np.float32), dt)
+    q_raw = synth.to_bits(rng.standard_normal((R, H, 192), np.float32) * np.float32(0.9), dt)
+    pos = [lens[0]] + [lens[1] + t for t in range(chunk)]
+    q_rot = q_raw.copy()
+    for r in range(R):
+        q_rot[r] = oracle.q_rope(q_raw[r], pos[r], 40.0, 4096, 10000.0, dt)
+    assert not np.array_equal(q_rot, q_raw)
+    outs = []
+    for in_kernel in (False, True):
+        ctx = make_ctx(case, capi.KERNEL_AUTO, max_rows=R)
+        seqs = fill(torch, ctx, case, upto=lens)
+        ctx.set_q_rope(in_kernel)
+        out = torch.zeros((R, H, 128), dtype=torch.int16, device="cuda")
+        ctx.step_begin(seqs, n_new)
+        ctx.step_layers(0, 1, _dev(torch, kv)[None], _dev(torch, q_raw if in_kernel else q_rot)[None], out[None])
+        ctx.step_end()
+        got = [_host(out).copy()]
+        # explicit-length call: the query stands at the last attended position
+        out2 = torch.zeros((2, H, 128), dtype=torch.int16, device="cuda")
+        sel = [0, R - 1]
+        ctx.attend_rows(0, seqs, [lens[0] + 1, lens[1] + chunk],
+                        _dev(torch, (q_raw if in_kernel else q_rot)[sel]), out2)
+        got.append(_host(out2).copy())
+        assert ctx.status() == 0
+        if in_kernel:                      # refused where a row has no position of its own
+            with pytest.raises(Exception):
+                ctx.step_begin(seqs, [0, 1])
+        outs.append(got)
+        if not in_kernel:
+            rows = oracle.append_rows(kv, pos, case.norm_w, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, dt)
+            cache1 = np.concatenate([case.caches[1][:lens[1]], rows[1:]])
+            want = oracle.attention(q_rot[R - 1], cache1, lens[1] + chunk, case.w_uk, case.w_uv, case.w_type, H, dt)
+            check_close(got[0][R - 1], want, dt, "last chunk row")
+        ctx.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    for k, r in enumerate([0, R - 1]):    # other split points, so equal only within the tolerance
+        check_close(outs[0][1][k], outs[0][0][r], dt, "explicit-length call")
+
+
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_prefill_chunk_is_causal(torch, oracle, kernel):
     """A 70-token chunk appended at start_position 50 next to a plain decode row: token t attends
