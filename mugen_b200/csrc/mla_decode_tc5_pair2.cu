@@ -77,13 +77,10 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 #define MLA_TRY_WAIT_HINT_NS 20000
 #endif
 constexpr uint32_t TRY_WAIT_HINT_NS = MLA_TRY_WAIT_HINT_NS;
-#ifndef MLA_PAIR128_PREFETCH
-#define MLA_PAIR128_PREFETCH 2
-#endif
-constexpr int PREFETCH_TILES = MLA_PAIR128_PREFETCH;                   // L2 prefetch distance, in super-tiles
 
-enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KEMPTY + NSUB, B_VEMPTY = B_VFULL + 4,
-       B_SFULL = B_VEMPTY + 4, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
+constexpr int K_ROUNDS = (NSUB + N_QK - 1) / N_QK;   // 3: the issuers free sub-tiles {0-3}, {4-7}, {8} together
+enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KEMPTY + K_ROUNDS, B_VEMPTY = B_VFULL + 4,
+       B_SFULL = B_VEMPTY + PAGES, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
 static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -192,14 +189,6 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
         ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
 
 // ---- tcgen05, cta_group::2 -----------------------------------------------------------------
 __device__ __forceinline__ bool elect_one() {
@@ -279,7 +268,10 @@ template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 #define TR_NOW(x) x = clock64()
 #define TR_ADD(acc, a, b) acc += (b) - (a)
 __device__ long long tr_buf[96];
-#define TR_EV(idx) do { if (blockIdx.x == 6 && blockIdx.y == 0 && t >= 50 && t < 53) tr_buf[(t - 50) * 32 + (idx)] = clock64(); } while (0)
+#ifndef MLA_TR_T0
+#define MLA_TR_T0 50
+#endif
+#define TR_EV(idx) do { if (blockIdx.x == 6 && blockIdx.y == 0 && t >= MLA_TR_T0 && t < MLA_TR_T0 + 3) tr_buf[(t - MLA_TR_T0) * 32 + (idx)] = clock64(); } while (0)
 #else
 #define TR_EV(idx)
 #define TR_DECL(...)
@@ -306,7 +298,7 @@ __device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __grid_constant__ CUtensorMap map_kv64,
-                          const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_page,
+                          const __grid_constant__ CUtensorMap map_q,
                           uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
                           float scale_log2, uint32_t* __restrict__ status)
 {
@@ -342,14 +334,10 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         need_flag[0] = need_flag[1] = 0;
         mbar_init(bar(B_QFULL), 1);
         mbar_init(bar(B_QEMPTY), N_QK);
-        for (int c = 0; c < NSUB; c++) {
-            mbar_init(bar(B_KFULL + c), 1);
-            mbar_init(bar(B_KEMPTY + c), 1);
-        }
-        for (int v = 0; v < 4; v++) {
-            mbar_init(bar(B_VFULL + v), 1);
-            mbar_init(bar(B_VEMPTY + v), 1);
-        }
+        for (int c = 0; c < NSUB; c++) mbar_init(bar(B_KFULL + c), 1);
+        for (int rd = 0; rd < K_ROUNDS; rd++) mbar_init(bar(B_KEMPTY + rd), min(N_QK, NSUB - N_QK * rd));
+        for (int v = 0; v < 4; v++) mbar_init(bar(B_VFULL + v), 1);
+        for (int pg = 0; pg < PAGES; pg++) mbar_init(bar(B_VEMPTY + pg), N_PV);
         mbar_init(bar(B_SFULL), N_QK);
         mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
@@ -405,29 +393,26 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                         page = 0;
                     }
                     const int slot0 = int(page * kPage);
+                    // The score issuers release the sub-tiles in rounds ({0-3}, {4-7}, {8}); one wait per round
+                    // instead of one per sub-tile: a shared-memory round trip costs this thread ~300 cycles while
+                    // the MMAs stream their operands, and nine of them per tile made it the slowest stage.
 #pragma unroll 1
-                    for (int c = 0; c < NSUB; c++) {
-                        if (c == 0) TR_EV(22);
-                        if (c == 5) TR_EV(31);
-                        ok = mbar_wait_cta(bar(B_KEMPTY + c), (t & 1) ^ 1, abort_flag, status);
+                    for (int rd = 0; rd < K_ROUNDS && ok; rd++) {
+                        ok = mbar_wait_cta(bar(B_KEMPTY + rd), (t & 1) ^ 1, abort_flag, status);
                         if (!ok) break;
-                        if (c == 5) TR_EV(23);
-                        if (c == 2) TR_EV(24);
-                        if (c == 3) TR_EV(25);
-                        if (c == 0) TR_EV(0);
-                        if (c == 4) TR_EV(1);
-                        if (c == 8) TR_EV(2);
-                        if (rank == 0) mbar_expect_tx(bar(B_KFULL + c), 2 * SUB_BYTES);
-                        if (c == 5) TR_EV(11);
-                        tma_load_3d_pair(sK + c * SUB_BYTES, &map_sub, leader_kfull + 8 * c, 64 * c, slot0, int(layer));
-                        if (c == 5) TR_EV(15);
+                        TR_EV(rd);
+#pragma unroll 1
+                        for (int c = N_QK * rd; c < min(N_QK * (rd + 1), NSUB); c++) {
+                            if (rank == 0) mbar_expect_tx(bar(B_KFULL + c), 2 * SUB_BYTES);
+                            tma_load_3d_pair(sK + c * SUB_BYTES, &map_sub, leader_kfull + 8 * c, 64 * c, slot0, int(layer));
+                        }
                     }
                 }
                 nseg++;
             }
         }
     } else if (warp == N_QK + N_PV + 1) {
-        // ===================== TMA producer for V, and L2 prefetch of later pages =====================
+        // ===================== TMA producer for V =====================
         if (lane == 0) {
             const uint32_t leader_vfull = map_to_rank(bar(B_VFULL), 0);
             uint32_t t = 0;
@@ -436,35 +421,23 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
-                // each block pulls "its" page of the first tiles into L2; the twin's V loads of that page hit there
-                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) {
-                    const uint32_t pg = page_of(tbl, s, jj, rank);
-                    if (pg < n_pages) tma_prefetch_4d(&map_page, 0, int(pg * kPage), 0, int(layer));
-                }
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
-                    const uint32_t pf = (PREFETCH_TILES > 0 && j + PREFETCH_TILES < s.n_tiles) ? page_of(tbl, s, j + PREFETCH_TILES, rank) : 0xffffffffu;
 #pragma unroll 1
-                    for (uint32_t v = 0; v < 4; v++) {          // v = 2 * page + chunk, the order the issuers consume them
-                        uint32_t page = page_of(tbl, s, j, v / 2);
+                    for (uint32_t pg = 0; pg < uint32_t(PAGES) && ok; pg++) {     // both chunk issuers release a page together
+                        uint32_t page = page_of(tbl, s, j, pg);
                         if (page >= n_pages) page = 0;           // flagged by the K producer
-                        ok = mbar_wait_cta(bar(B_VEMPTY + v), (t & 1) ^ 1, abort_flag, status);
+                        ok = mbar_wait_cta(bar(B_VEMPTY + pg), (t & 1) ^ 1, abort_flag, status);
                         if (!ok) break;
-                        TR_EV(3 + v);
-                        if (rank == 0) mbar_expect_tx(bar(B_VFULL + v), 2 * VBUF_BYTES);
-                        // all 64 tokens of the page, this block's 128 dims of chunk v%2 = sub-tiles 4*(v%2) + 2r, +1
-#ifdef MLA_PAIR128_ONE_MAP
-                        {
-                            const int c0 = 4 * int(v % 2) + 2 * int(rank);
-                            tma_load_3d_pair(sV + v * VBUF_BYTES, &map_sub, leader_vfull + 8 * v, 64 * c0, int(page * kPage), int(layer));
-                            tma_load_3d_pair(sV + v * VBUF_BYTES + SUB_BYTES, &map_sub, leader_vfull + 8 * v, 64 * (c0 + 1),
-                                             int(page * kPage), int(layer));
+                        TR_EV(3 + pg);
+#pragma unroll 1
+                        for (uint32_t ch = 0; ch < 2; ch++) {
+                            const uint32_t v = 2 * pg + ch;
+                            if (rank == 0) mbar_expect_tx(bar(B_VFULL + v), 2 * VBUF_BYTES);
+                            // all 64 tokens of the page, this block's 128 dims of chunk ch = sub-tiles 4*ch + 2r, +1
+                            tma_load_4d_pair(sV + v * VBUF_BYTES, &map_kv64, leader_vfull + 8 * v, 0, int(page * kPage),
+                                             4 * int(ch) + 2 * int(rank), int(layer));
                         }
-#else
-                        tma_load_4d_pair(sV + v * VBUF_BYTES, &map_kv64, leader_vfull + 8 * v, 0, int(page * kPage),
-                                         4 * int(v % 2) + 2 * int(rank), int(layer));
-#endif
                     }
-                    if (pf < n_pages) tma_prefetch_4d(&map_page, 0, int(pf * kPage), 0, int(layer));
                 }
             }
         }
@@ -509,7 +482,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                                 for (int k = 0; k < 4; k++)
                                     tc_mma_pair(d, qk_a + ((c * SUB_BYTES + k * 32) >> 4), HI, qk_b + ((c * SUB_BYTES + k * 32) >> 4),
                                                 HI, IDESC_QK, (c == part && k == 0) ? 0u : 1u);
-                                tc_commit_pair(bar(B_KEMPTY + c));
+                                tc_commit_pair(bar(B_KEMPTY + c / N_QK));
                                 if (c + N_QK >= uint32_t(NSUB)) {      // same thread as the MMAs it covers
                                     tc_commit_pair(bar(B_SFULL));
                                     if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
@@ -543,7 +516,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                                 for (int k = 0; k < kPage / 16; k++)
                                     tc_mma_pair(tmem + COL_O + part * (2 * HG), pv_a + ((v * VBUF_BYTES + k * 2048) >> 4), HI,
                                                 pv_b + ((pg * P_BYTES + k * 32) >> 4), HI, IDESC_PV, k == 0 ? fresh : 1u);
-                                tc_commit_pair(bar(B_VEMPTY + v));
+                                tc_commit_pair(bar(B_VEMPTY + pg));
                                 if (pg + 1 == uint32_t(PAGES)) {
                                     tc_commit_pair(bar(B_PEMPTY));
                                     if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_OFULL));
@@ -663,15 +636,18 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 TR_NOW(c2);
                 TR_ADD(tr_ld, c1, c2);
                 if (st_id == 0) TR_EV(17);
+                // Scores stay unscaled in registers: the scale rides in the FMA in front of each exponential, and
+                // the mask pass runs only on a segment's last, partly filled tile.
                 const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
+                if (valid < uint32_t(TILE)) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (tq * 32 + uint32_t(i) >= valid) sv[i] = __float_as_uint(-INFINITY);
+                }
                 float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float v = __uint_as_float(sv[i]) * scale_log2;
-                    v = (tq * 32 + uint32_t(i) < valid) ? v : -INFINITY;
-                    sv[i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
+                for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+                mx *= scale_log2;
                 // does any head of the pair have to move its reference maximum on this tile?
                 const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
                 const bool warp_need = __any_sync(0xffffffffu, need);
@@ -692,8 +668,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
-                    const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                    const float p0 = fast_ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -m_used));
+                    const float p1 = fast_ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -m_used));
                     sum += p0 + p1;
                     pk[i / 2] = Elem<T>::pack2(p0, p1);
                 }
@@ -731,8 +707,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     sum = 0.0f;
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = fast_ex2(__uint_as_float(sv[i]) - m_used);
-                        const float p1 = fast_ex2(__uint_as_float(sv[i + 1]) - m_used);
+                        const float p0 = fast_ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -m_used));
+                        const float p1 = fast_ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -m_used));
                         sum += p0 + p1;
                         pk[i / 2] = Elem<T>::pack2(p0, p1);
                     }
@@ -831,14 +807,14 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 #ifdef MLA_TC5_TRACE
     if (blockIdx.x == 6 && blockIdx.y == 0 && tid == 0) {
-        const char* names[32] = {"K0 issue", "K4 issue", "K8 issue", "V0 issue", "V1 issue", "V2 issue", "V3 issue", "QK sempty", "QK kfull0",
+        const char* names[32] = {"K round0", "K round1", "K round2", "V page0", "V page1", "-", "-", "QK sempty", "QK kfull0",
                                  "QK kfull4", "QK kfull8", "K5 expected", "PV pfull", "PV vfull0", "PV vfull2", "K5 issued", "SM sfull", "SM ld", "SM exp",
                                  "SM synca", "SM pempty", "SM pfull", "K0 wait", "K5 waited", "K2 issue", "K3 issue", "QK done0", "QK done4",
                                  "QK done8", "PV done0", "PV done1", "K5 begin"};
         const long long o = tr_buf[16];
         for (int tt = 0; tt < 3; tt++)
             for (int i = 0; i < 32; i++)
-                if (names[i][0] != '-') printf("EV t=%d %-10s %lld\n", 50 + tt, names[i], tr_buf[tt * 32 + i] - o);
+                if (names[i][0] != '-') printf("EV t=%d %-10s %lld\n", MLA_TR_T0 + tt, names[i], tr_buf[tt * 32 + i] - o);
     }
 #endif
     if (warp == 1) {
@@ -865,7 +841,7 @@ int decode_tc5_pair128_configure()
 }
 
 // tmaps: [0] pool, box 64 values x 64 tokens (one K sub-tile); [4] pool whole-row view, box 64 tokens x 2 chunks (V);
-// [5] absorbed queries, box 64 rows x 9 chunks; [6] pool whole-row view, box 64 tokens x 9 chunks (L2 prefetch of a page).
+// [5] absorbed queries, box 64 rows x 9 chunks.
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
                               float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
 {
@@ -875,9 +851,9 @@ int launch_decode_tc5_pair128(int dtype, const void* tmaps, uint32_t layer, uint
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
         return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4], maps[5],
-                              maps[6], layer, n_pages, m, recs, H, scale_log2, status));
+                              layer, n_pages, m, recs, H, scale_log2, status));
     return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4],
-                          maps[5], maps[6], layer, n_pages, m, recs, H, scale_log2, status));
+                          maps[5], layer, n_pages, m, recs, H, scale_log2, status));
 }
 
 }  // namespace mla
