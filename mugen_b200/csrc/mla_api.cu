@@ -336,7 +336,8 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     const bool timed = c->profiling && c->prof_used < c->prof_events.size() && (c->prof_seq++ % c->prof_stride) == 0;
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
-        e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
+        e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer_pool(c, layer), layer, c->cfg.n_pages, m, c->recs, H,
+                                           c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05_PAIR)
         e = mla::launch_decode_tc5_pair(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)

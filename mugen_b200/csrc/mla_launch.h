@@ -35,9 +35,9 @@ int decode_tc5_configure();   // sets the kernel's shared-memory attribute once
 int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
                            float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
 int decode_tc5_pair_configure();
-// same contract, 128-token tiles (two pages per score MMA series); uses tmaps [0], [4], [5], [6]
-int launch_decode_tc5_pair128(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
-                              float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
+// same contract, 128-token tiles (two pages per score MMA series); uses tmaps [0], [4], [5] and the layer's pool slice
+int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
+                              const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
 int decode_tc5_pair128_configure();
 
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
