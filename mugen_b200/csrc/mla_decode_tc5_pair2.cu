@@ -18,17 +18,18 @@
 // shared segment must start 1 KB-aligned because there is no slack to round up (checked; the
 // status word says so if not).
 //
-// TMEM: O^T 2 x 128 columns; scores in 2 buffers x 2 partial tiles of 64 columns.  Four warps
-// issue the score MMAs (a warp waits ~50-100 cycles per MMA it issues, so four are needed to keep
-// the pipe busy); issuers p and p+2 accumulate into the same partial tile, p's first MMA
-// overwrites it and p+2 waits for that MMA to be issued (B_SINIT, between the two tcgen05 fences).
-// With the score tile double-buffered the next tile's QK runs while the softmax works.
+// TMEM: O^T 2 x 128 columns; four partial score tiles of 64 columns, one per issuing warp (a warp
+// waits ~50-100 cycles per MMA it issues, so four of them are needed to keep the pipe busy).  Each
+// accumulator has ONE issuing thread and the softmax adds the partials in a fixed order, so the
+// result is bit-reproducible from run to run and under any page permutation.  (A variant with two
+// partials shared by two issuers each and the score tile double-buffered took the same time and
+// lost that property: the order of the accumulations then depends on timing.)
 //
 // Warps: 0 K producer, 1-4 score issuers (sub-tiles {0,4,8} {1,5} {2,6} {3,7}), 5-6 value issuers
 // (one per chunk), 7 V producer (+ optional linear L2 prefetch of later pages), 8-15 softmax.  The
-// softmax writes its optimistic P (exponentials against the current reference maximum) before the
-// cluster round that tells whether any head of the pair must move its maximum has returned; only
-// in that rare case P is rewritten and O^T rescaled.  Waiting threads sleep in the barrier unit
+// softmax computes its exponentials optimistically against the current reference maximum while the
+// cluster round that tells whether any head of the pair must move its maximum is in flight; only
+// in that rare case they are redone and O^T rescaled.  Waiting threads sleep in the barrier unit
 // (try_wait with a time hint) rather than re-poll: shared-memory bandwidth is what the MMA operand
 // fetches and the TMA fills compete for.  All waits are bounded.
 //
@@ -78,8 +79,7 @@ constexpr int M_LSUM = 1536;      // [3][64] floats: the other quarters' partial
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0;       // 2 chunks x 128 head columns
-constexpr uint32_t COL_S = 256;     // 2 buffers x 2 partial score tiles x 64 columns
-constexpr int S_PARTS = 2;          // issuers p and p+2 accumulate into partial p%2
+constexpr uint32_t COL_S = 256;     // 4 partial score tiles x 64 columns
 
 constexpr int N_QK = 4, N_PV = 2;
 constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 8);   // 512
@@ -104,7 +104,7 @@ constexpr uint32_t TRY_WAIT_HINT_NS = MLA_TRY_WAIT_HINT_NS;
 constexpr int PREFETCH_TILES = MLA_PAIR128_PREFETCH;
 constexpr int K_ROUNDS = (NSUB + N_QK - 1) / N_QK;   // 3: the issuers free sub-tiles {0-3}, {4-7}, {8} together
 enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KEMPTY + K_ROUNDS, B_VEMPTY = B_VFULL + 4,
-       B_SFULL0 = B_VEMPTY + PAGES, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_SINIT0, B_SINIT1, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
+       B_SFULL = B_VEMPTY + PAGES, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
 static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -367,11 +367,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         for (int rd = 0; rd < K_ROUNDS; rd++) mbar_init(bar(B_KEMPTY + rd), min(N_QK, NSUB - N_QK * rd));
         for (int v = 0; v < 4; v++) mbar_init(bar(B_VFULL + v), 1);
         for (int pg = 0; pg < PAGES; pg++) mbar_init(bar(B_VEMPTY + pg), N_PV);
-        for (int b = 0; b < 2; b++) {
-            mbar_init(bar(B_SFULL0 + b), N_QK);
-            mbar_init(bar(B_SEMPTY0 + b), PAIR_SOFTMAX_WARPS);
-            mbar_init(bar(B_SINIT0 + b), 1);
-        }
+        mbar_init(bar(B_SFULL), N_QK);
+        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
         mbar_init(bar(B_PEMPTY), N_PV);
         mbar_init(bar(B_OFULL), N_PV);
@@ -501,22 +498,18 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
                     if (is_qk) {
-                        // sub-tiles part, part+4 (, part+8).  Issuers p and p+2 accumulate into the same partial tile
-                        // p%2 of score buffer t%2: p starts it (its first MMA overwrites), p+2 may only add once that
-                        // MMA has been issued, which p announces through B_SINIT between the two tcgen05 fences.
-                        const uint32_t sb = t & 1, q2 = part % S_PARTS;
+                        // sub-tiles part, part+4 (, part+8): partial scores into this warp's own 64 columns
                         TR_NOW(c0);
-                        ok = mbar_wait(bar(B_SEMPTY0 + sb), ((t >> 1) & 1) ^ 1, abort_flag, status);
+                        ok = mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
                         TR_NOW(c1);
                         TR_ADD(tr_a, c0, c1);
                         if (part == 0 && lane == 0) TR_EV(7);
                         if (!ok) break;
-                        const uint32_t d = tmem + COL_S + sb * (S_PARTS * TILE / 2) + q2 * (TILE / 2);
+                        const uint32_t d = tmem + COL_S + part * (TILE / 2);
 #pragma unroll 1
                         for (uint32_t c = part; c < uint32_t(NSUB); c += N_QK) {
                             TR_NOW(c0);
                             ok = mbar_wait(bar(B_KFULL + c), t & 1, abort_flag, status);
-                            if (ok && part >= uint32_t(S_PARTS) && c == part) ok = mbar_wait_cta(bar(B_SINIT0 + q2), t & 1, abort_flag, status);
                             TR_NOW(c1);
                             TR_ADD(tr_b, c0, c1);
                             if (part == 0 && lane == 0) TR_EV(8 + c / 4);
@@ -526,14 +519,10 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
 #pragma unroll
                                 for (int k = 0; k < 4; k++)
                                     tc_mma_pair(d, qk_a + ((c * SUB_BYTES + k * 32) >> 4), HI, qk_b + ((c * SUB_BYTES + k * 32) >> 4),
-                                                HI, IDESC_QK, (part < uint32_t(S_PARTS) && c == part && k == 0) ? 0u : 1u);
-                                if (part < uint32_t(S_PARTS) && c == part) {
-                                    tc_fence_before();
-                                    mbar_arrive_cta(bar(B_SINIT0 + q2));
-                                }
+                                                HI, IDESC_QK, (c == part && k == 0) ? 0u : 1u);
                                 tc_commit_pair(bar(B_KEMPTY + c / N_QK));
                                 if (c + N_QK >= uint32_t(NSUB)) {      // same thread as the MMAs it covers
-                                    tc_commit_pair(bar(B_SFULL0 + sb));
+                                    tc_commit_pair(bar(B_SFULL));
                                     if (j + 1 == s.n_tiles) tc_commit_pair(bar(B_QEMPTY));
                                 }
                             }
@@ -600,7 +589,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         const uint32_t hl = 32 * (q4 % 2) + lane;             // head within this block's 64
         const uint32_t st_id = tid - (NUM_THREADS - SOFTMAX_THREADS);
         const uint32_t peer = rank ^ 1;
-        const uint32_t r_sempty[2] = {map_to_rank(bar(B_SEMPTY0), 0), map_to_rank(bar(B_SEMPTY1), 0)};
+        const uint32_t r_sempty = map_to_rank(bar(B_SEMPTY), 0);
         const uint32_t r_pfull = map_to_rank(bar(B_PFULL), 0);
         const uint32_t r_synca[2] = {map_to_rank(bar(B_SYNCA0), peer), map_to_rank(bar(B_SYNCA1), peer)};
         const uint32_t r_syncb[2] = {map_to_rank(bar(B_SYNCB0), peer), map_to_rank(bar(B_SYNCB1), peer)};
@@ -653,7 +642,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t par = t & 1;
                 TR_NOW(c0);
-                wait_w(bar(B_SFULL0 + par), (t >> 1) & 1);
+                wait_w(bar(B_SFULL), t & 1);
                 TR_NOW(c1);
                 TR_ADD(tr_sfull, c0, c1);
                 if (st_id == 0) TR_EV(16);
@@ -662,9 +651,16 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     tc_fence_after();
                     {
                         uint32_t sw[32];
-                        const uint32_t sbase = tmem + lane_base + COL_S + par * (S_PARTS * TILE / 2) + grp * 32;
-                        tc_ld32(sbase, sv);
-                        tc_ld32(sbase + (TILE / 2), sw);
+                        tc_ld32(tmem + lane_base + COL_S + grp * 32, sv);
+                        tc_ld32(tmem + lane_base + COL_S + (TILE / 2) + grp * 32, sw);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
+                    }
+#pragma unroll 1
+                    for (int p = 2; p < N_QK; p++) {
+                        uint32_t sw[32];
+                        tc_ld32(tmem + lane_base + COL_S + p * (TILE / 2) + grp * 32, sw);
                         tc_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i++) sv[i] = __float_as_uint(__uint_as_float(sv[i]) + __uint_as_float(sw[i]));
@@ -672,8 +668,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {                       // orders only TMEM reads: no memory release needed
-                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY0 + par));
-                        else mbar_arrive_cluster_relaxed(r_sempty[par]);
+                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY));
+                        else mbar_arrive_cluster_relaxed(r_sempty);
                     }
                 } else {
 #pragma unroll
@@ -722,34 +718,15 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 TR_NOW(c3);
                 TR_ADD(tr_exp, c2, c3);
                 if (st_id == 0) TR_EV(18);
-                // row hl of the page's K-major swizzled P tile, this thread's 32 tokens = 16-byte chunks 4*grp .. 4*grp+3
-                auto write_p = [&]() {
-                    unsigned char* prow = sm + OFF_P + half * P_BYTES + hl * 128;
-#pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {
-                        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-                        *reinterpret_cast<uint4*>(prow + (((4 * grp + ch) ^ (hl & 7)) << 4)) = v;
-                    }
-                };
-                // PV of the previous tile must be complete: O is stable and P is free.  The optimistic P goes
-                // out first; the cluster round has usually finished by the time it is written.
-                wait_w(bar(B_PEMPTY), (t - 1) & 1);
-                TR_NOW(c4);
-                TR_ADD(tr_pempty, c3, c4);
-                if (st_id == 0) TR_EV(20);
-                if (!fail) {
-                    tc_fence_after();
-                    write_p();
-                }
                 wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
                 if (group_or(fail)) { stop = true; break; }
-                TR_NOW(c5);
-                TR_ADD(tr_synca, c4, c5);
+                TR_NOW(c4);
+                TR_ADD(tr_synca, c3, c4);
                 if (st_id == 0) TR_EV(19);
                 const bool slow = need_flag[par] != 0;
                 if (slow) {
                     // exchange the token quarters' maxima inside the block, decide per head, publish the
-                    // scale factors to both blocks, redo the exponentials and P, rescale O
+                    // scale factors to both blocks, and redo the exponentials
                     float alpha = 1.0f;
                     half_max[tq * HG + hl] = mx;
                     group_or(false);
@@ -777,32 +754,45 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                         sum += p0 + p1;
                         pk[i / 2] = Elem<T>::pack2(p0, p1);
                     }
-                    if (!fail) {
-                        write_p();
-                        if (j > 0) {
-                            // O^T[this block's dims][128 heads] *= alpha[head]; each warp group takes one chunk
-#pragma unroll 1
-                            for (int c = 0; c < 4; c++) {
-                                uint32_t o[32];
-                                const uint32_t col = COL_O + grp * 128 + c * 32;
-                                tc_ld32(tmem + lane_base + col, o);
-                                tc_wait_ld();
-                                const float* al = alpha_all + par * 128 + c * 32;
-#pragma unroll
-                                for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * al[i]);
-                                tc_st32(tmem + lane_base + col, o);
-                            }
-                            tc_wait_st();
-                        }
-                    }
                 }
                 l_part += sum;
+                // PV of the previous tile must be complete: O is stable and P is free
+                TR_NOW(c5);
+                TR_ADD(tr_slow, c4, c5);
+                wait_w(bar(B_PEMPTY), (t - 1) & 1);
                 TR_NOW(c6);
-                TR_ADD(tr_slow, c5, c6);
+                TR_ADD(tr_pempty, c5, c6);
+                if (st_id == 0) TR_EV(20);
+                if (fail) continue;            // carried to the next barrier
+                tc_fence_after();
+                if (slow && j > 0) {
+                    // O^T[this block's dims][128 heads] *= alpha[head]; each warp group takes one chunk
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t o[32];
+                        const uint32_t col = COL_O + grp * 128 + c * 32;
+                        tc_ld32(tmem + lane_base + col, o);
+                        tc_wait_ld();
+                        const float* al = alpha_all + par * 128 + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * al[i]);
+                        tc_st32(tmem + lane_base + col, o);
+                    }
+                    tc_wait_st();
+                }
+                {
+                    // row hl of the page's K-major swizzled P tile, this thread's 32 tokens = 16-byte chunks 4*grp .. 4*grp+3
+                    unsigned char* prow = sm + OFF_P + half * P_BYTES + hl * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                        *reinterpret_cast<uint4*>(prow + (((4 * grp + ch) ^ (hl & 7)) << 4)) = v;
+                    }
+                }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0 && !fail) {
+                if (lane == 0) {
                     if (rank == 0) mbar_arrive_cta(bar(B_PFULL));
                     else mbar_arrive_remote(r_pfull);
                 }
