@@ -35,7 +35,7 @@ from mugen_b200 import synth  # noqa: E402
 METRIC, UNIT = "mla_decode_tokens_per_s", "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at the default workload
 # (profiles/decode_tc5_pair128_kernel_v3shape_b64_ctx16384.md); only meaningful for that workload and kernel
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.2514e9
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.2491e9
 NCU_TRAFFIC_KERNEL = "tcgen05-pair128"
 # The attention kernel is timed live by CUDA events inside the library on every 7th launch of the timed region
 # (7 is coprime to 61 layers, so every layer gets sampled over the steps): an event between two kernels stops
