@@ -326,7 +326,7 @@ def run_ours(a):
         e2e = {"value": tokens / (float(et[0]) * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(world * L * (B * 576 * 2 + B * H * 192 * 2)),
                "d2h_bytes_per_step": int(world * L * B * H * 128 * 2),
-               "api": "mla_step_begin / mla_step_layer_host (page-locked host buffers) / mla_step_end, stream synchronised every step"}
+               "api": "mla_step_begin / mla_step_layer_host (page-locked host buffers, copies on the context's copy streams overlap the layers' kernels) / mla_step_end (returns when the outputs are on the host), stream synchronised every step"}
         assert ctx.status() == 0
 
     cpu = None

@@ -162,11 +162,12 @@ int mla_step_attend(mla_ctx* ctx, uint32_t layer, const void* q, void* out, void
  * [n_layers][rows][n_heads][128].  Same kernels and order as the per-layer calls. */
 int mla_step_layers(mla_ctx* ctx, uint32_t layer_begin, uint32_t n_layers, const void* kv_a,
                     const void* q, void* out, void* stream);
-/* Same two calls with HOST buffers: copies kv_a and q in, runs append + attend, copies out
- * back, all on `stream`.  Page-locked caller buffers are copied directly and the call returns
- * without waiting (synchronise the stream, or call mla_status, before reading out_host);
- * pageable buffers are staged through page-locked memory inside the context and the call
- * returns when out_host is filled. */
+/* Same two calls with HOST buffers: copies kv_a and q in, runs append + attend on `stream`, copies
+ * out back.  Page-locked caller buffers are copied directly on two copy streams of the context, so
+ * the next layer's inputs and the previous layer's outputs move while a layer computes; the call
+ * returns without waiting, the host buffers must hold their data when it is made, and out_host is
+ * complete when mla_step_end returns.  Pageable buffers are staged through page-locked memory
+ * inside the context and the call returns when out_host is filled. */
 int mla_step_layer_host(mla_ctx* ctx, uint32_t layer, const void* kv_a_host, const void* q_host,
                         void* out_host, void* stream);
 int mla_step_end(mla_ctx* ctx);

@@ -90,6 +90,11 @@ struct mla_ctx {
 
     // host-buffer entry point staging
     void *h_in = nullptr, *h_out = nullptr, *d_kv = nullptr, *d_q = nullptr, *d_out = nullptr;
+    // page-locked callers: copies run on two streams of their own so that layer L+1's inputs and layer L-1's
+    // outputs move while layer L computes; one event triple per layer orders copy-in -> compute -> copy-out
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    struct HostEv { cudaEvent_t in = nullptr, compute = nullptr, out = nullptr; bool used = false, pending = false; };
+    std::vector<HostEv> host_ev;
 };
 
 namespace {
@@ -647,6 +652,9 @@ void mla_destroy(mla_ctx* c)
     if (c->h_in) cudaFreeHost(c->h_in);
     if (c->h_out) cudaFreeHost(c->h_out);
     cudaFree(c->d_kv); cudaFree(c->d_q); cudaFree(c->d_out);
+    for (auto& ev : c->host_ev) { cudaEventDestroy(ev.in); cudaEventDestroy(ev.compute); cudaEventDestroy(ev.out); }
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
     delete c;
 }
 
@@ -914,12 +922,31 @@ int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const
     char* d_out = static_cast<char*>(c->d_out) + layer * o_cap;
     const bool direct = is_pinned(kv_a_host) && is_pinned(q_host) && is_pinned(out_host);
     if (direct) {
-        // page-locked caller buffers: fully asynchronous, the caller synchronises the stream
-        // (or calls mla_status) before reading out_host
-        CU_TRY(c, cudaMemcpyAsync(d_kv, kv_a_host, kv_b, cudaMemcpyHostToDevice, st));
-        CU_TRY(c, cudaMemcpyAsync(d_q, q_host, q_b, cudaMemcpyHostToDevice, st));
+        // page-locked caller buffers: fully asynchronous; out_host is complete when mla_step_end returns
+        if (!c->copy_in) {
+            CU_TRY(c, cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+            CU_TRY(c, cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+            c->host_ev.resize(L);
+            for (auto& ev : c->host_ev) {
+                CU_TRY(c, cudaEventCreateWithFlags(&ev.in, cudaEventDisableTiming));
+                CU_TRY(c, cudaEventCreateWithFlags(&ev.compute, cudaEventDisableTiming));
+                CU_TRY(c, cudaEventCreateWithFlags(&ev.out, cudaEventDisableTiming));
+            }
+        }
+        auto& ev = c->host_ev[layer];
+        // this layer's device slots were last read / written by its previous use
+        if (ev.used) CU_TRY(c, cudaStreamWaitEvent(c->copy_in, ev.compute, 0));
+        CU_TRY(c, cudaMemcpyAsync(d_kv, kv_a_host, kv_b, cudaMemcpyHostToDevice, c->copy_in));
+        CU_TRY(c, cudaMemcpyAsync(d_q, q_host, q_b, cudaMemcpyHostToDevice, c->copy_in));
+        CU_TRY(c, cudaEventRecord(ev.in, c->copy_in));
+        CU_TRY(c, cudaStreamWaitEvent(st, ev.in, 0));
+        if (ev.used) CU_TRY(c, cudaStreamWaitEvent(st, ev.out, 0));
         if (int e = run_layer(c, layer, d_kv, d_q, d_out, st)) return e;
-        CU_TRY(c, cudaMemcpyAsync(out_host, d_out, o_b, cudaMemcpyDeviceToHost, st));
+        CU_TRY(c, cudaEventRecord(ev.compute, st));
+        CU_TRY(c, cudaStreamWaitEvent(c->copy_out, ev.compute, 0));
+        CU_TRY(c, cudaMemcpyAsync(out_host, d_out, o_b, cudaMemcpyDeviceToHost, c->copy_out));
+        CU_TRY(c, cudaEventRecord(ev.out, c->copy_out));
+        ev.used = ev.pending = true;
         return MLA_OK;
     }
     if (!c->h_in) {
@@ -944,6 +971,11 @@ int mla_step_end(mla_ctx* c)
     if (!c) return MLA_ERR_INVALID;
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_end without step_begin");
     c->in_step = false;
+    for (auto& ev : c->host_ev)              // outputs of mla_step_layer_host must have landed in the caller's buffers
+        if (ev.pending) {
+            CU_TRY(c, cudaEventSynchronize(ev.out));
+            ev.pending = false;
+        }
     for (size_t i = 0; i < c->step_seqs.size(); i++)
         if (int e = pt_code(c, c->pt->advance(c->step_seqs[i], c->step_nnew[i]))) return e;
     return MLA_OK;

@@ -454,6 +454,51 @@ def test_host_buffer_entry_point(torch, oracle, kernel):
     ctx.close()
 
 
+def test_host_buffer_entry_point_page_locked_overlaps_and_matches_device_path(torch):
+    """Page-locked caller buffers: copies run on the context's own copy streams (inputs of the next
+    layer and outputs of the previous one move while a layer computes).  Two steps over three
+    layers must give, bit for bit, what the device-buffer call gives, and the outputs must be in
+    the host buffers when step_end returns."""
+    H, L, dt, lens = 128, 3, synth.DT_BF16, [300, 65]
+    case = synth.make_layer_case(91, H, [n + 2 for n in lens], dt)
+    rng = np.random.default_rng(6)
+    kv = [synth.to_bits(rng.standard_normal((L, 2, 576), np.float32), dt) for _ in range(2)]
+    q = [synth.to_bits(rng.standard_normal((L, 2, H, 192), np.float32) * np.float32(0.9), dt) for _ in range(2)]
+    results = []
+    for mode in ("device", "host"):
+        ctx = make_ctx(case, capi.KERNEL_AUTO, n_layers=L)
+        seqs = []
+        for b, n in enumerate(lens):
+            s_ = ctx.seq_create()
+            for l in range(L):
+                ctx.write_rows(l, s_, 0, _dev(torch, case.caches[b][:n]))
+            ctx.advance_seq_len(s_, n)
+            seqs.append(s_)
+        outs = []
+        for step in range(2):
+            if mode == "device":
+                out = torch.zeros((L, 2, H, 128), dtype=torch.int16, device="cuda")
+                ctx.step_begin(seqs)
+                ctx.step_layers(0, L, _dev(torch, kv[step]), _dev(torch, q[step]), out)
+                ctx.step_end()
+                outs.append(_host(out).copy())
+            else:
+                hkv = torch.from_numpy(kv[step].view(np.int16)).pin_memory()
+                hq = torch.from_numpy(q[step].view(np.int16)).pin_memory()
+                hout = torch.zeros((L, 2, H, 128), dtype=torch.int16).pin_memory()
+                ctx.step_begin(seqs)
+                for l in range(L):
+                    ctx.step_layer_host(l, hkv[l], hq[l], hout[l])
+                ctx.step_end()                      # no stream synchronisation: step_end waits for the copies
+                outs.append(hout.numpy().view(np.uint16).copy())
+        assert ctx.status() == 0
+        results.append(outs)
+        ctx.close()
+    for step in range(2):
+        assert results[1][step].any()
+        assert np.array_equal(results[0][step], results[1][step])
+
+
 # ---------------------------------------------------------------------------------------------
 # bookkeeping and error behaviour on the device-backed context
 # ---------------------------------------------------------------------------------------------
