@@ -181,7 +181,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
         for (int s = 0; s < kRank / 64; s++) tma_load_2d(sW + s * W_SUB, &map_w, bar_w, 64 * s, int(h) * kVDim);
     }
 
-    // Reduction of the partial states, one warp per four rows, two rows at a time.  A lane owns dims
+    // Reduction of the partial states, one warp per four rows (16 apart), two rows at a time.  A lane owns dims
     // 64*k + 2*lane (+1), k = 0..3, of the current half: a warp load covers 256 contiguous bytes of
     // a state record and a warp store one whole 128-byte operand row.  Parts are taken four at a
     // time with the usual running-maximum update, so the (m, l) pass and the accumulation are one
@@ -189,10 +189,13 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     constexpr uint32_t IDESC = instr_desc(Fmt<T>::v, MT, kVDim);
     bool ok = true;
     grid_dependency_wait();          // W_UV is constant and already on its way; the partial states are not
+    // A warp's four rows are warp, warp+16, warp+32, warp+48 of the block's 64: with a small batch (8 sequences
+    // per GPU when the batch is sharded over 8) every row then has a warp of its own instead of two warps
+    // walking all of them; a row of such a batch is cut into ~10 parts, three round trips to memory each half.
     uint32_t pb4[4], pe4[4];                              // part ranges of this warp's four rows
 #pragma unroll
     for (int x = 0; x < 4; x++) {
-        const uint32_t rw = r0 + 4 * warp + x;
+        const uint32_t rw = r0 + warp + 16 * x;
         pb4[x] = pe4[x] = 0;
         if (rw < rows) {
             if (row_seg_begin) { pb4[x] = row_seg_begin[rw]; pe4[x] = row_seg_begin[rw + 1]; }
@@ -207,7 +210,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
             float M[2], L[2], acc[2][8];
 #pragma unroll
             for (int x = 0; x < 2; x++) {
-                rw[x] = r0 + 4 * warp + 2 * pr + x;
+                rw[x] = r0 + warp + 16 * (2 * pr + x);
                 p[x] = pr == 0 ? pb4[x] : pb4[2 + x];
                 pe[x] = pr == 0 ? pe4[x] : pe4[2 + x];
                 M[x] = -INFINITY;
@@ -263,7 +266,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
 #pragma unroll
             for (int x = 0; x < 2; x++) {
                 const float inv = L[x] > 0.0f ? 1.0f / L[x] : 0.0f;
-                const uint32_t rr = 4 * warp + 2 * pr + x;
+                const uint32_t rr = warp + 16 * (2 * pr + x);
                 const uint32_t off = rr * 128 + (((lane / 4) ^ (rr & 7)) << 4) + (lane % 4) * 4;
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
