@@ -213,7 +213,7 @@ def run_ours(a):
     H, L = a.heads, a.layers
     dt = synth.DT_BF16 if a.dtype == "bf16" else synth.DT_F16
     tdt = torch.bfloat16 if a.dtype == "bf16" else torch.float16
-    kernel = {"auto": capi.KERNEL_AUTO, "mma": capi.KERNEL_MMA, "tcgen05": capi.KERNEL_TCGEN05, "tcgen05-pair": capi.KERNEL_TCGEN05_PAIR, "tcgen05-pair128": capi.KERNEL_TCGEN05_PAIR128}[a.kernel]
+    kernel = {"auto": capi.KERNEL_AUTO, "mma": capi.KERNEL_MMA, "tcgen05": capi.KERNEL_TCGEN05, "tcgen05-pair128": capi.KERNEL_TCGEN05_PAIR128}[a.kernel]
     total_steps = a.warmup + a.steps + (0 if a.no_e2e else a.warmup + a.steps)
     start_len = a.ctx - 1 - a.warmup          # the first timed step attends exactly ctx rows
     pages_per_seq = (start_len + total_steps + 64 + 63) // 64

@@ -50,10 +50,9 @@ enum { MLA_W_F16 = 1, MLA_W_Q4_0 = 2, MLA_W_Q8_0 = 8, MLA_W_BF16 = 30 };
 
 /* Split-KV attention kernel family (mla_config.kernel).  AUTO picks PAIR128 when n_heads is a multiple of
  * 128 (SM pairs, tcgen05.mma.cta_group::2, 128-token tiles), TCGEN05 for other head counts >= 64 (one SM per
- * 64 heads) and MMA (mma.sync m16n8k16) below that; PAIR is the 64-token-tile SM-pair kernel.  All give the
- * same results within the attention tolerance; each is bit-reproducible from run to run. */
-enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2, MLA_KERNEL_TCGEN05_PAIR = 3,
-       MLA_KERNEL_TCGEN05_PAIR128 = 4 };
+ * 64 heads) and MMA (mma.sync m16n8k16) below that.  All give the same results within the attention
+ * tolerance; each is bit-reproducible from run to run. */
+enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2, MLA_KERNEL_TCGEN05_PAIR128 = 3 };
 
 /* Shape contract: the MLA fields of mugen::ModelConfig (src/core/model/transformer.h:65-79)
  * plus the paged-pool geometry the reference lacks (it keeps one contiguous
@@ -211,7 +210,7 @@ int mla_launch_count(const mla_ctx* ctx, uint64_t* n);
  * then clears the record. */
 int mla_profile_enable(mla_ctx* ctx, int on);
 int mla_profile_read(mla_ctx* ctx, uint32_t* launches, float* total_ms);
-/* Name of the attention kernel family in use ("mma", "tcgen05", "tcgen05-pair", "tcgen05-pair128"). */
+/* Name of the attention kernel family in use ("mma", "tcgen05", "tcgen05-pair128"). */
 const char* mla_kernel_name(const mla_ctx* ctx);
 /* Reads `n` latent rows [row_begin, row_begin+n) of (layer, seq) back to HOST memory. */
 int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
@@ -225,19 +224,20 @@ int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_b
 /* ---- for callers that may not allocate ------------------------------------------------------ */
 /* No counterpart in the reference.  Absorbed MLA attention of one query row over one CONTIGUOUS
  * latent cache, without a context and without any allocation: no cudaMalloc, cudaFree or
- * allocating library routine is called, now or later.  For callers whose device memory is owned
- * by someone else's pool, or that must not trigger cudaMalloc's device-wide synchronisation.
- * Intermediates live in an 8.2 MiB array built into the library (held on every GPU the process
- * uses until exit), hence the limits n_heads <= 128 and seq_len <= 65536; larger sizes return
- * MLA_ERR_CAPACITY.  All pointers are DEVICE pointers in `dtype`:
+ * allocating library routine is called, now or later, and nothing is copied from host memory.
+ * For callers whose device memory is owned by someone else's pool, or that must not trigger
+ * cudaMalloc's device-wide synchronisation.  Intermediates live in an 8.2 MiB array built into the
+ * library (held on every GPU the process uses until exit), hence the limits n_heads <= 128 and
+ * seq_len <= 65536; larger sizes return MLA_ERR_CAPACITY.  All pointers are DEVICE pointers in `dtype`:
  *   q     [n_heads][192]  post-RoPE query (nope first)     out  [n_heads][128]
- *   cache [seq_len rounded up to a multiple of 64][576]   rows past seq_len are read, never used:
- *                                                         they must be mapped and hold finite values
+ *   cache [seq_len][576]  exactly seq_len rows: nothing behind the last row is read
  *   w_uk, w_uv  (n_heads*128) x 512 row-major, as the reference keeps them (transformer.cpp:3178-3221)
- * The first call on a device resolves the array's address (cudaGetSymbolAddress) and sets a
- * kernel attribute; make it before any stream capture.  Calls that overlap on one GPU race on
- * the shared array: serialise them.  Asynchronous on `stream`.  mla_noalloc_last_error() gives
- * the text of the calling thread's last failure. */
+ * The first call on a device resolves the array's address (cudaGetSymbolAddress) and sets kernel
+ * attributes on that device; make that first call outside any stream capture.  Calls that overlap
+ * on one GPU race on the shared array: serialise them.  Asynchronous on `stream`.  The device status
+ * word of the context entry points has no reader here: a fault inside a kernel of this path is not
+ * reported (argument errors are, through the return code).  mla_noalloc_last_error() gives the text
+ * of the calling thread's last failure. */
 int mla_attention_noalloc(uint32_t dtype, uint32_t n_heads, uint32_t seq_len, const void* q,
                           const void* cache, const void* w_uk, const void* w_uv, void* out,
                           void* stream);

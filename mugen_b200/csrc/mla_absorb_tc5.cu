@@ -14,13 +14,14 @@
 // bit-exact RMSNorm + RoPE + scatter of append_kernel (mla_kernels.cu), 128 threads per row.  They
 // share the launch because the append is a chain of dependent float additions that takes as long
 // as the absorb itself and needs only a handful of SMs.
-#include <cuda.h>
-
 #include "mla_launch.h"
+#include "mla_tc5.cuh"
 
 namespace mla {
 
 namespace {
+
+using namespace tc5;
 
 constexpr int MT = 64;                          // query rows per absorb block
 constexpr int W_SUB = kRank * 128;              // 65,536: [512 d][64 i]
@@ -37,88 +38,7 @@ constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // + slack to round t
 constexpr int NUM_THREADS = 512;
 constexpr int APPEND_ROWS = NUM_THREADS / 128;  // rows per append block
 constexpr uint32_t TMEM_COLS = 512;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded: gives up after about two seconds, raises the status bit and tells the block through `fail_flag`
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* fail_flag, uint32_t* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*fail_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *fail_flag = 1;
-                atomicOr(status, ST_WAIT_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "setp.ne.b32 p, %6, 0;\n"
-        "mov.b64 da, {%1, %2};\n"
-        "mov.b64 db, {%3, %4};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// shared-memory matrix descriptor halves (K-major, 128-byte swizzle, 8-row groups 1 KB apart)
-__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
-constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 
 struct AppendArgs {          // rows == 0: no append blocks in this launch
     const void* kv_a;
@@ -289,8 +209,8 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
                 for (int s = 0; s < 2; s++) {
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        tc_mma(tmem + half * 256, desc_lo(sA + s * A_SUB + k * 32), DESC_HI,
-                               desc_lo(sW + s * W_SUB + half * (W_SUB / 2) + k * 32), DESC_HI, IDESC, (s == 0 && k == 0) ? 0u : 1u);
+                        tc_mma(tmem + half * 256, desc_lo(sA + s * A_SUB + k * 32), desc_hi(1024),
+                               desc_lo(sW + s * W_SUB + half * (W_SUB / 2) + k * 32), desc_hi(1024), IDESC, (s == 0 && k == 0) ? 0u : 1u);
                 }
             }
             tc_commit(bar_mma);

@@ -65,10 +65,8 @@ struct mla_ctx {
     uint32_t max_segs = 0;
     uint32_t workers = 1;
     uint32_t* status_dev = nullptr;
-    // tensor maps of the tcgen05 attention kernels (make_tensor_maps): [0] cache pool, box 64 values x 64 tokens;
-    // [1] absorbed queries; [2] cache pool, 32-token box; [3..6] whole-row views of pool and queries (all sub-tiles
-    // of a row range in ONE box)
-    alignas(64) CUtensorMap tmaps[7];
+    // tensor maps of the tcgen05 attention kernels (make_tensor_maps; indices mla::kMap*)
+    alignas(64) CUtensorMap tmaps[mla::kMapCount];
 
     // metadata upload ring
     MetaBuf ring[kMetaRing];
@@ -112,6 +110,10 @@ int fail(mla_ctx* c, int code, std::string msg)
         if (e__ != cudaSuccess)                                                                   \
             return fail((c), MLA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
     } while (0)
+
+// Every entry point that launches or copies makes the context's device current first: a host thread that
+// drives several contexts (one per GPU) would otherwise launch on whichever device it used last.
+#define USE_DEVICE(c) CU_TRY((c), cudaSetDevice((c)->cfg.device))
 
 int pt_code(mla_ctx* c, int e)
 {
@@ -343,11 +345,8 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
         e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer_pool(c, layer), layer, c->cfg.n_pages, m, c->recs, H,
                                            c->status_dev, st);
-    else if (c->kernel == MLA_KERNEL_TCGEN05_PAIR)
-        e = mla::launch_decode_tc5_pair(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)
-        e = mla::launch_decode_tc5(int(c->cfg.dtype), c->q_abs, c->tmaps, layer, c->cfg.n_pages, m,
-                                   c->recs, H, c->status_dev, st);
+        e = mla::launch_decode_tc5(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else
         e = mla::launch_decode_mma(int(c->cfg.dtype), c->q_abs, layer_pool(c, layer), c->cfg.n_pages, m,
                                    c->recs, H, c->status_dev, st);
@@ -427,41 +426,26 @@ int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row
 
 int make_tensor_maps(mla_ctx* c)
 {
-    // cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda.
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    CU_TRY(c, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (!fn || qres != cudaDriverEntryPointSuccess)
-        return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const CUtensorMapDataType dt = c->cfg.dtype == MLA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                  : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    const cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    auto encode = [&](int slot, const char* what, cuuint32_t rank, void* basep, const cuuint64_t* dims,
+                      const cuuint64_t* strides, const cuuint32_t* box) -> int {
+        const CUresult r = enc(&c->tmaps[slot], dt, rank, basep, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(c, MLA_ERR_CUDA, std::string("cuTensorMapEncodeTiled(") + what + ") failed with code " + std::to_string(int(r)));
+        return MLA_OK;
+    };
     {   // cache pool: 576 values innermost, then the token slots of a layer, then layers;
         // box = 64 values (128 B, one swizzle row) x 64 tokens (one page)
         const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
         const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
         const cuuint32_t box[3] = {64, 64, 1};
-        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[0], dt, 3, c->pool, dims, strides, box, estr,
-                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS)
-            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool) failed with code " + std::to_string(int(r)));
-    }
-    {   // the same pool with a 32-token box, for the SM-pair kernel (each block stages half a page of K)
-        const cuuint64_t dims[3] = {cuuint64_t(mla::kRow), c->pool_slots, c->cfg.n_layers};
-        const cuuint64_t strides[2] = {cuuint64_t(mla::kRow) * 2, c->pool_slots * mla::kRow * 2};
-        const cuuint32_t box[3] = {64, 32, 1};
-        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[2], dt, 3, c->pool, dims, strides, box, estr,
-                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS)
-            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool, half page) failed with code " + std::to_string(int(r)));
+        if (int e = encode(mla::kMapPoolSub, "cache pool", 3, c->pool, dims, strides, box)) return e;
     }
     // Whole-row views: the 576 values of a row are exposed as (64 values, 9 chunks) with the chunk
     // dimension OUTSIDE the row dimension, so one box {64 values, R rows, C chunks} lands in shared
@@ -470,38 +454,14 @@ int make_tensor_maps(mla_ctx* c)
     {
         const cuuint64_t dims[4] = {64, c->pool_slots, 9, c->cfg.n_layers};
         const cuuint64_t strides[3] = {cuuint64_t(mla::kRow) * 2, 128, c->pool_slots * mla::kRow * 2};
-        const cuuint32_t estr4[4] = {1, 1, 1, 1};
-        const cuuint32_t boxes[3][4] = {{64, 32, 9, 1}, {64, 64, 2, 1}, {64, 64, 9, 1}};
-        const int slot[3] = {3, 4, 6};
-        for (int i = 0; i < 3; i++) {
-            CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[slot[i]], dt, 4, c->pool, dims, strides, boxes[i], estr4,
-                                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS)
-                return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(cache pool, whole-row view " + std::to_string(i) +
-                                                 ") failed with code " + std::to_string(int(r)));
-        }
+        const cuuint32_t box_v[4] = {64, 64, 2, 1}, box_page[4] = {64, 64, 9, 1};
+        if (int e = encode(mla::kMapPoolV, "cache pool, two chunks of a page", 4, c->pool, dims, strides, box_v)) return e;
+        if (int e = encode(mla::kMapPoolPage, "cache pool, whole page", 4, c->pool, dims, strides, box_page)) return e;
+        // 64 spare rows behind the queries: boxes of 64 head rows may start at the last row's heads
         const cuuint64_t qdims[3] = {64, cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64, 9};
         const cuuint64_t qstrides[2] = {cuuint64_t(mla::kRow) * 2, 128};
         const cuuint32_t qbox[3] = {64, 64, 9};
-        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[5], dt, 3, c->q_abs, qdims, qstrides, qbox, estr,
-                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS)
-            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(queries, whole-row view) failed with code " + std::to_string(int(r)));
-    }
-    {   // absorbed queries [max_rows * heads][576]; box = 64 values x 64 head rows
-        const cuuint64_t dims[2] = {cuuint64_t(mla::kRow), cuuint64_t(c->cfg.max_rows) * c->cfg.n_heads + 64};
-        const cuuint64_t strides[1] = {cuuint64_t(mla::kRow) * 2};
-        const cuuint32_t box[2] = {64, 64};
-        CUresult r = reinterpret_cast<EncodeFn>(fn)(&c->tmaps[1], dt, 2, c->q_abs, dims, strides, box, estr,
-                                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS)
-            return fail(c, MLA_ERR_CUDA, "cuTensorMapEncodeTiled(queries) failed with code " + std::to_string(int(r)));
+        if (int e = encode(mla::kMapQueries, "absorbed queries", 3, c->q_abs, qdims, qstrides, qbox)) return e;
     }
     return MLA_OK;
 }
@@ -560,7 +520,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
               : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
               : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA;
     const uint32_t H = cfg->n_heads;
-    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR || c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
+    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
     else c->workers = std::max<uint32_t>(1, c->sm_count * 2 / ((H + 15) / 16));
 
@@ -598,12 +558,13 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
         CR_TRY(cudaMallocHost(&mb.host, c->meta_cap));
         CR_TRY(cudaEventCreateWithFlags(&mb.done, cudaEventDisableTiming));
     }
-    if (c->kernel == MLA_KERNEL_TCGEN05_PAIR) {
-        if (int rc = make_tensor_maps(cp)) return bail(rc);
-        if (int ce = mla::decode_tc5_pair_configure()) {
-            cp->err = std::string("tcgen05 pair kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
-            return bail(MLA_ERR_CUDA);
-        }
+    if (int ce = mla::decode_mma_configure()) {
+        cp->err = std::string("mma attention kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
+    }
+    if (int ce = mla::merge_mma_configure()) {
+        cp->err = std::string("mma merge kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
     }
     if (int ce = mla::absorb_tc5_configure()) {
         cp->err = std::string("tcgen05 absorb kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
@@ -663,6 +624,7 @@ const char* mla_last_error(const mla_ctx* c) { return c ? c->err.c_str() : g_cre
 int mla_status(mla_ctx* c, void* stream, uint32_t* device_status)
 {
     if (!c || !device_status) return MLA_ERR_INVALID;
+    USE_DEVICE(c);
     auto st = static_cast<cudaStream_t>(stream);
     uint32_t v = 0;
     CU_TRY(c, cudaMemcpyAsync(&v, c->status_dev, 4, cudaMemcpyDeviceToHost, st));
@@ -703,15 +665,41 @@ int mla_seq_create(mla_ctx* c, uint32_t* id)
     if (!c || !id) return MLA_ERR_INVALID;
     return pt_code(c, c->pt->seq_create(id));
 }
-int mla_seq_free(mla_ctx* c, uint32_t id) { return c ? pt_code(c, c->pt->seq_free(id)) : MLA_ERR_INVALID; }
+// While a step is open its uploaded block tables name the sequences' pages: giving pages back (or moving a
+// counter the step is about to move) in between would let another sequence take pages the kernels still read.
+static int refuse_in_step(mla_ctx* c, const char* what)
+{
+    return fail(c, MLA_ERR_STATE, std::string(what) + " is not allowed while a step is open");
+}
+int mla_seq_free(mla_ctx* c, uint32_t id)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (c->in_step) return refuse_in_step(c, "seq_free");
+    return pt_code(c, c->pt->seq_free(id));
+}
 int mla_seq_len(const mla_ctx* c, uint32_t id, uint32_t* len)
 {
     if (!c || !len) return MLA_ERR_INVALID;
     return c->pt->seq_len(id, len);
 }
-int mla_advance(mla_ctx* c, uint32_t id, uint32_t n) { return c ? pt_code(c, c->pt->advance(id, n)) : MLA_ERR_INVALID; }
-int mla_truncate(mla_ctx* c, uint32_t id, uint32_t n) { return c ? pt_code(c, c->pt->truncate(id, n)) : MLA_ERR_INVALID; }
-int mla_clear(mla_ctx* c, uint32_t id) { return c ? pt_code(c, c->pt->clear(id)) : MLA_ERR_INVALID; }
+int mla_advance(mla_ctx* c, uint32_t id, uint32_t n)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (c->in_step) return refuse_in_step(c, "advance");
+    return pt_code(c, c->pt->advance(id, n));
+}
+int mla_truncate(mla_ctx* c, uint32_t id, uint32_t n)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (c->in_step) return refuse_in_step(c, "truncate");
+    return pt_code(c, c->pt->truncate(id, n));
+}
+int mla_clear(mla_ctx* c, uint32_t id)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (c->in_step) return refuse_in_step(c, "clear");
+    return pt_code(c, c->pt->clear(id));
+}
 int mla_seq_set_base(mla_ctx* c, uint32_t id, uint32_t base) { return c ? pt_code(c, c->pt->set_base(id, base)) : MLA_ERR_INVALID; }
 int mla_free_pages(const mla_ctx* c, uint32_t* n)
 {
@@ -739,6 +727,7 @@ int mla_append_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_
                     const void* kv_a, void* stream)
 {
     if (!c || (n && (!seq_ids || !positions || !kv_a))) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (int e = check_layer(c, layer, true)) return e;
     if (c->in_step) return fail(c, MLA_ERR_STATE, "explicit-position calls are not allowed while a step is open");
     if (n > c->cfg.max_rows) return fail(c, MLA_ERR_CAPACITY, "more rows than max_rows");
@@ -764,6 +753,7 @@ int mla_attend_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_
                     const void* q, void* out, void* stream)
 {
     if (!c || (n && (!seq_ids || !attend_lens || !q || !out))) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (int e = check_layer(c, layer, true)) return e;
     if (c->in_step) return fail(c, MLA_ERR_STATE, "explicit-position calls are not allowed while a step is open");
     if (n > c->cfg.max_rows) return fail(c, MLA_ERR_CAPACITY, "more rows than max_rows");
@@ -793,6 +783,7 @@ int mla_attend_rows(mla_ctx* c, uint32_t layer, uint32_t n, const uint32_t* seq_
 int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const uint32_t* n_new, void* stream)
 {
     if (!c || (n_seq && !seq_ids)) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (c->in_step) return fail(c, MLA_ERR_STATE, "step_begin while a step is open");
     auto st = static_cast<cudaStream_t>(stream);
     std::vector<uint32_t> seqs(seq_ids, seq_ids + n_seq);
@@ -839,6 +830,7 @@ int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const ui
 int mla_step_append(mla_ctx* c, uint32_t layer, const void* kv_a, void* stream)
 {
     if (!c || !kv_a) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_append outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     return run_append(c, layer, kv_a, static_cast<cudaStream_t>(stream));
@@ -847,6 +839,7 @@ int mla_step_append(mla_ctx* c, uint32_t layer, const void* kv_a, void* stream)
 int mla_step_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, void* stream)
 {
     if (!c || !q || !out) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_attend outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     return run_attend(c, layer, q, out, nullptr, static_cast<cudaStream_t>(stream));
@@ -856,6 +849,7 @@ int mla_step_layers(mla_ctx* c, uint32_t layer_begin, uint32_t n_layers, const v
                     void* stream)
 {
     if (!c || !kv_a || !q || !out) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layers outside step_begin/step_end");
     if (uint64_t(layer_begin) + n_layers > c->cfg.n_layers) return fail(c, MLA_ERR_INVALID, "layer range out of bounds");
     auto st = static_cast<cudaStream_t>(stream);
@@ -873,6 +867,7 @@ int mla_step_layers(mla_ctx* c, uint32_t layer_begin, uint32_t n_layers, const v
 int mla_step_attend_partial(mla_ctx* c, uint32_t layer, const void* q, float* partial, void* stream)
 {
     if (!c || !q || !partial) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_attend_partial outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     return run_attend(c, layer, q, nullptr, partial, static_cast<cudaStream_t>(stream));
@@ -882,6 +877,7 @@ int mla_merge_partials(mla_ctx* c, uint32_t layer, uint32_t n_parts, uint32_t ro
                        void* out, void* stream)
 {
     if (!c || !partials || !out || n_parts == 0) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (int e = check_layer(c, layer, true)) return e;
     if (int rc = run_merge(c, layer, partials, nullptr, n_parts, out, nullptr, rows, static_cast<cudaStream_t>(stream)))
         return rc;
@@ -904,6 +900,7 @@ int mla_step_layer_host(mla_ctx* c, uint32_t layer, const void* kv_a_host, const
                         void* stream)
 {
     if (!c || !kv_a_host || !q_host || !out_host) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layer_host outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     auto st = static_cast<cudaStream_t>(stream);
@@ -970,15 +967,22 @@ int mla_step_end(mla_ctx* c)
 {
     if (!c) return MLA_ERR_INVALID;
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_end without step_begin");
+    // The step closes and the counters move whatever happens below (the rows were written by kernels already
+    // queued); the first error is reported after that.
     c->in_step = false;
+    int rc = MLA_OK;
+    cudaSetDevice(c->cfg.device);
     for (auto& ev : c->host_ev)              // outputs of mla_step_layer_host must have landed in the caller's buffers
         if (ev.pending) {
-            CU_TRY(c, cudaEventSynchronize(ev.out));
+            const cudaError_t e = cudaEventSynchronize(ev.out);
+            if (e != cudaSuccess && rc == MLA_OK)
+                rc = fail(c, MLA_ERR_CUDA, std::string("cudaEventSynchronize(output copy): ") + cudaGetErrorString(e));
             ev.pending = false;
         }
     for (size_t i = 0; i < c->step_seqs.size(); i++)
-        if (int e = pt_code(c, c->pt->advance(c->step_seqs[i], c->step_nnew[i]))) return e;
-    return MLA_OK;
+        if (int e = pt_code(c, c->pt->advance(c->step_seqs[i], c->step_nnew[i])))
+            if (rc == MLA_OK) rc = e;
+    return rc;
 }
 
 int mla_step_info(const mla_ctx* c, uint32_t* rows, uint32_t* segments)
@@ -1007,6 +1011,7 @@ int mla_set_q_rope(mla_ctx* c, int in_kernel)
 int mla_profile_enable(mla_ctx* c, int on)
 {
     if (!c) return MLA_ERR_INVALID;
+    USE_DEVICE(c);
     if (on && c->prof_events.empty()) {
         c->prof_events.resize(8192);
         for (auto& pe : c->prof_events) {
@@ -1023,6 +1028,7 @@ int mla_profile_enable(mla_ctx* c, int on)
 int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
 {
     if (!c || !launches || !total_ms) return MLA_ERR_INVALID;
+    USE_DEVICE(c);
     float sum = 0.0f;
     for (size_t i = 0; i < c->prof_used; i++) {
         CU_TRY(c, cudaEventSynchronize(c->prof_events[i].second));
@@ -1039,12 +1045,13 @@ int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
 const char* mla_kernel_name(const mla_ctx* c)
 {
     if (!c) return "";
-    return c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? "tcgen05-pair128" : c->kernel == MLA_KERNEL_TCGEN05_PAIR ? "tcgen05-pair" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
+    return c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? "tcgen05-pair128" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
 }
 
 int mla_read_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, void* host_out, void* stream)
 {
     if (!c || !host_out) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (int e = check_layer(c, layer, false)) return e;
     const auto* s = c->pt->seq(id);
     if (!s) return fail(c, MLA_ERR_INVALID, "unknown sequence id");
@@ -1068,6 +1075,7 @@ int mla_write_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, 
                    void* stream)
 {
     if (!c || (n && !dev_rows)) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
     if (int e = check_layer(c, layer, false)) return e;
     if (!c->pt->seq(id)) return fail(c, MLA_ERR_INVALID, "unknown sequence id");
     if (c->in_step) return fail(c, MLA_ERR_STATE, "write_rows is not allowed while a step is open");

@@ -34,8 +34,9 @@ constexpr size_t SMEM_TOTAL = SMEM_KV + SMEM_SP + SMEM_PS + 16 * 4;
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+// copies 16 bytes, or writes 16 zero bytes without touching `src` when `live` is false
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(live ? 16u : 0u));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -116,11 +117,15 @@ decode_mma_kernel(const T* __restrict__ q_abs, const T* __restrict__ pool, uint3
             const T* src = pool + (size_t(page) * kPage + tok % kPage) * kRow;
             T* dst = kv + size_t(tile % NS) * TT * KV_PITCH;
             constexpr int kChunksPerRow = kRow / 8;   // 72
+            // rows at or past the segment's end are zero-filled, not read: a caller's cache may end with its last
+            // row, and whatever lies behind a sequence's end need not be finite (P = 0 times NaN is NaN)
+            const uint32_t live_rows = n_tok - tile * TT;            // > 0 here; >= TT for all but the last tile
 #pragma unroll
             for (int k = 0; k < TT * kChunksPerRow / 128; k++) {
                 const int c = tid + 128 * k;
                 const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
-                cp_async16(smem_u32(dst + r * KV_PITCH + cc * 8), src + size_t(r) * kRow + cc * 8);
+                const bool live = uint32_t(r) < live_rows;
+                cp_async16(smem_u32(dst + r * KV_PITCH + cc * 8), src + (live ? size_t(r) * kRow + cc * 8 : 0), live);
             }
         }
         cp_async_commit();
@@ -254,20 +259,20 @@ decode_mma_kernel(const T* __restrict__ q_abs, const T* __restrict__ pool, uint3
 
 }  // namespace
 
+// Function attributes belong to a device: called once per device (context creation, first use of the
+// no-allocation entry point on a device), with that device current.
+int decode_mma_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_TOTAL));
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(decode_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_TOTAL));
+    return int(e);
+}
+
 int launch_decode_mma(int dtype, const void* q_abs, const void* layer_pool, uint32_t n_pages,
                       const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
 {
     if (m.segs == 0) return 0;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<__half>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_TOTAL));
-        if (e != cudaSuccess) return int(e);
-        e = cudaFuncSetAttribute(decode_mma_kernel<__nv_bfloat16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_TOTAL));
-        if (e != cudaSuccess) return int(e);
-        configured = true;
-    }
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(m.segs, (H + 15) / 16);
     if (dtype == 0)

@@ -25,16 +25,14 @@
 //
 // Every mbarrier wait is bounded: after ~2 s a waiter raises ST_WAIT_TIMEOUT in the status word,
 // sets the block's abort flag and every role leaves its loops; TMEM is freed on all paths.
-#include <cuda.h>
-#ifdef MLA_TC5_TRACE
-#include <cstdio>
-#endif
-
 #include "mla_launch.h"
+#include "mla_tc5.cuh"
 
 namespace mla {
 
 namespace {
+
+using namespace tc5;
 
 constexpr int TILE = 64;                          // tokens per tile = one page
 constexpr int HG = 64;                            // heads per block
@@ -60,173 +58,11 @@ constexpr int N_QK = 4, N_PV = 2;                 // MMA-issuing warps for QK an
 constexpr int NUM_THREADS = 32 * (1 + N_QK + N_PV + 4);   // producer + issuers + 4 softmax warps
 constexpr int SOFTMAX_THREADS = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
 // barrier slots inside the misc area (8 bytes each)
 enum { B_QFULL = 0, B_QEMPTY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL0, B_SFULL1,
        B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY, B_OFULL, B_COUNT };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-// ---- mbarrier ------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the block is aborting (either this waiter gave up or
-// another role raised the flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicOr(status, ST_WAIT_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// ---- TMA -----------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                            int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-// Pulls a box into L2 only: issued a few tiles ahead so that, when a shared-memory stage frees
-// up, the real load is an L2 hit and the stage turns around in hundreds of cycles, not thousands.
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
-                                            int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-
-// ---- tcgen05 -------------------------------------------------------------------------------
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-// The MMA-issuing thread is a single lane: every instruction it spends on building operands
-// delays the tensor core.  Descriptors are therefore kept as (low word, constant high word)
-// pairs; advancing an operand is one 32-bit add on the low word (address field, 16-byte units).
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "setp.ne.b32 p, %6, 0;\n"
-        "mov.b64 da, {%1, %2};\n"
-        "mov.b64 db, {%3, %4};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-// 16 lanes x 256 bits, repeated 8 times along the columns (64 columns): thread i receives, for
-// block k, registers 4k..4k+3 = (lane i/4, cols 8k+2(i%4), +1) and (lane i/4+8, same cols).
-__device__ __forceinline__ void tc_ld16x256_x8(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ float fast_ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
-//   K-major : rows of 128 B (64 elements of K), 8-row groups 1024 B apart (SBO); LBO unused.
-//   MN-major: rows of 128 B (64 elements of M/N) indexed by K, 8-row groups SBO apart,
-//             64-element M/N blocks LBO apart.
-// Low word: start address (bits 0-13, 16-byte units) and leading byte offset (bits 16-29).
-// High word: stride byte offset (bits 0-13), version 1 (bit 14), SWIZZLE_128B = 2 (bits 29-31).
-__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
-    return ((addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
-}
-__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
-    return (sbo_bytes >> 4) | (1u << 14) | (2u << 29);
-}
-// Instruction descriptor, kind::f16, f32 accumulate.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
-                                                  uint32_t b_mn_major) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
-           ((m >> 4) << 24);
-}
-
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 
 struct SegInfo {
     uint32_t row, page_begin, n_tiles, n_tok;
@@ -298,10 +134,6 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
         if (lane == 0) {
             uint32_t t = 0, nseg = 0;
             bool ok = true;
-#ifdef MLA_TC5_TRACE
-            long long trace_prod_wait = 0;
-            const long long trace_t0 = clock64();
-#endif
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
@@ -319,13 +151,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
                     if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
-#ifdef MLA_TC5_TRACE
-                    const long long tw0 = clock64();
-#endif
                     ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
-#ifdef MLA_TC5_TRACE
-                    trace_prod_wait += clock64() - tw0;
-#endif
                     if (!ok) break;
                     uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
@@ -338,10 +164,6 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 }
                 nseg++;
             }
-#ifdef MLA_TC5_TRACE
-            if (blockIdx.x == 3 && blockIdx.y == 0)
-                printf("[producer] tiles %u total %lld wait_kv_empty %lld\n", t, clock64() - trace_t0, trace_prod_wait);
-#endif
         }
     } else if (warp <= N_QK + N_PV) {
         // ===================== MMA issuers =====================
@@ -455,10 +277,6 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
             return v + __shfl_xor_sync(0xffffffffu, v, 2);
         };
         bool stop = false;
-#ifdef MLA_TC5_TRACE
-        long long tr_wait_s = 0, tr_compute = 0, tr_wait_p = 0, tr_store = 0, tr_rescales = 0;
-        const long long tr_s0 = clock64();
-#endif
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
             const SegInfo s = load_seg(m, seg);
             if (s.n_tiles == 0) {
@@ -477,14 +295,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t sb = t & 1;
                 float* alpha_t = alpha_s + sb * HG;
-#ifdef MLA_TC5_TRACE
-                const long long ts0 = clock64();
-#endif
                 wait_w(bar(B_SFULL0), t & 1);
-#ifdef MLA_TC5_TRACE
-                const long long ts1 = clock64();
-                tr_wait_s += ts1 - ts0;
-#endif
                 uint32_t sv[32];
                 if (!fail) {
                     tc_fence_after();
@@ -557,16 +368,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 l_a = l_a * alpha_a + quad_sum(sum_a);
                 l_b = l_b * alpha_b + quad_sum(sum_b);
                 // PV of the previous tile must be complete: O is stable and P is free
-#ifdef MLA_TC5_TRACE
-                const long long ts2 = clock64();
-                tr_compute += ts2 - ts1;
-#endif
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
-#ifdef MLA_TC5_TRACE
-                const long long ts3 = clock64();
-                tr_wait_p += ts3 - ts2;
-                if (any_need && j > 0) tr_rescales++;
-#endif
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
                 if (any_need && j > 0) {
@@ -598,9 +400,6 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(bar(B_PFULL));
-#ifdef MLA_TC5_TRACE
-                tr_store += clock64() - ts3;
-#endif
             }
             if (stop) break;
             // ---- epilogue of the segment: O^T -> acc[head][dim], plus (m, l)
@@ -634,11 +433,6 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
             tc_fence_before();
             nseg++;
         }
-#ifdef MLA_TC5_TRACE
-        if (blockIdx.x == 3 && blockIdx.y == 0 && tid == NUM_THREADS - SOFTMAX_THREADS)
-            printf("[softmax] tiles %u total %lld wait_s_full %lld compute %lld wait_p_empty %lld rescale+store %lld rescales %lld\n",
-                   t, clock64() - tr_s0, tr_wait_s, tr_compute, tr_wait_p, tr_store, tr_rescales);
-#endif
     }
 
     tc_fence_before();
@@ -661,20 +455,19 @@ int decode_tc5_configure()
     return int(e);
 }
 
-int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t layer, uint32_t n_pages,
-                      const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
+int launch_decode_tc5(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m, float* recs,
+                      uint32_t H, uint32_t* status, cudaStream_t st)
 {
-    (void)q_abs;
     if (m.ctas == 0) return 0;
-    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);   // whole-row views: [6] = cache pool, [5] = Q'
+    const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(m.ctas, (H + HG - 1) / HG);
     if (dtype == 0)
-        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[6], maps[5], layer, n_pages, m, recs, H,
-                                                                        scale_log2, status);
+        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries], layer, n_pages, m,
+                                                                        recs, H, scale_log2, status);
     else
-        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[6], maps[5], layer, n_pages, m,
-                                                                               recs, H, scale_log2, status);
+        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries], layer,
+                                                                               n_pages, m, recs, H, scale_log2, status);
     return int(cudaGetLastError());
 }
 

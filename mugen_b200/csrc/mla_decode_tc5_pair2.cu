@@ -33,21 +33,19 @@
 // (try_wait with a time hint) rather than re-poll: shared-memory bandwidth is what the MMA operand
 // fetches and the TMA fills compete for.  All waits are bounded.
 //
-// What bounds it, measured with clock64 and %globaltimer inside the kernel (-DMLA_TC5_TRACE): about
+// What bounds it, measured with clock64 and %globaltimer inside a traced build of the kernel: about
 // 400k SM cycles per launch at batch 64 x ctx 16384 at an effective SM clock of 1.55 GHz, although
 // nvidia-smi reports 1.97 GHz around a short run: the clock is throttled within the kernel, and
 // variants of this kernel that need fewer or more cycles (prefetch on or off, polling hints, score
 // double-buffering, producer layouts) all take the same 260-275 us.
-#include <cuda.h>
-#ifdef MLA_TC5_TRACE
-#include <cstdio>
-#endif
-
 #include "mla_launch.h"
+#include "mla_tc5.cuh"
 
 namespace mla {
 
 namespace {
+
+using namespace tc5;
 
 constexpr int PAGES = 2;                            // pages per super-tile
 constexpr int TILE = PAGES * kPage;                 // 128 tokens
@@ -86,13 +84,6 @@ constexpr int NUM_THREADS = 32 * (2 + N_QK + N_PV + 8);   // 512
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int PAIR_SOFTMAX_WARPS = 16;
 constexpr float RESCALE_THRESHOLD = 8.0f;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
-// A waiting thread sleeps in the barrier unit until the phase completes or this long, instead of
-// re-polling shared memory, whose bandwidth the MMA operand fetches need.
-#ifndef MLA_TRY_WAIT_HINT_NS
-#define MLA_TRY_WAIT_HINT_NS 20000
-#endif
-constexpr uint32_t TRY_WAIT_HINT_NS = MLA_TRY_WAIT_HINT_NS;
 
 // L2 prefetch distance in tiles (0 = off): every block pulls "its" whole page towards L2 that many tiles ahead as
 // ONE linear request of 73,728 contiguous bytes, so DRAM sees a sequential burst per page instead of thirteen
@@ -107,206 +98,6 @@ enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KE
        B_SFULL = B_VEMPTY + PAGES, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
 static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-// shared::cluster address of `addr` (a shared::cta address of this block) in block `rank`
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-
-// ---- mbarrier ------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-// default semantics (release at block scope) on the twin block's barrier: what orders this block's
-// own shared-memory writes before the signal, without a cluster-wide release
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_cta(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cta(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
-    if (mbar_try_cta(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_cta(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicOr(status, ST_WAIT_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicOr(status, ST_WAIT_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// ---- TMA (no multicast; .cta_group::2 only lets the completion land on the pair leader's barrier)
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
-                                                 int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
-                                                 int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
-// contiguous bytes towards L2 (address and size multiples of 16)
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gptr), "r"(bytes) : "memory");
-}
-
-// ---- tcgen05, cta_group::2 -----------------------------------------------------------------
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-// completion of all MMAs issued so far by this thread -> the barrier at this offset in BOTH blocks
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
-                 ::"r"(bar), "h"(uint16_t(3)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                            uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "setp.ne.b32 p, %6, 0;\n"
-        "mov.b64 da, {%1, %2};\n"
-        "mov.b64 db, {%3, %4};\n"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ float fast_ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// shared-memory matrix descriptor halves (128-byte swizzle, version 1); see mla_decode_tc5.cu
-__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
-    return ((addr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
-}
-__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
-
-#ifdef MLA_TC5_TRACE
-#define TR_DECL(...) long long __VA_ARGS__
-#define TR_NOW(x) x = clock64()
-#define TR_ADD(acc, a, b) acc += (b) - (a)
-__device__ long long tr_buf[96];
-#ifndef MLA_TR_T0
-#define MLA_TR_T0 50
-#endif
-#define TR_EV(idx) do { if (blockIdx.x == 6 && blockIdx.y == 0 && t >= MLA_TR_T0 && t < MLA_TR_T0 + 3) tr_buf[(t - MLA_TR_T0) * 32 + (idx)] = clock64(); } while (0)
-#else
-#define TR_EV(idx)
-#define TR_DECL(...)
-#define TR_NOW(x)
-#define TR_ADD(acc, a, b)
-#endif
 
 struct SegInfo {
     uint32_t row, page_begin, n_pages, n_tiles, n_tok;
@@ -352,12 +143,13 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
 
     // The swizzled operand tiles need 1 KB alignment and the plan leaves no room to round up.
     // Both blocks of a pair see the same offset, so they take this exit together.
+    grid_launch_dependents();
     if ((base & 1023u) != 0) {
+        grid_dependency_wait();          // also this exit keeps the stream's "every kernel waits before it completes" chain
         if (tid == 0) atomicOr(status, ST_BAD_ALIGNMENT);
         return;
     }
 
-    grid_launch_dependents();
     if (tid == 0) {
         *abort_flag = 0;
         need_flag[0] = need_flag[1] = 0;
@@ -411,7 +203,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
-                ok = mbar_wait_cta(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
+                ok = mbar_wait<kSleep>(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
                 tma_load_3d_pair(sQ, &map_q, leader_qfull, 0, int(s.row * H + h0), 0);      // all 9 sub-tiles at once
@@ -427,9 +219,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     // the MMAs stream their operands, and nine of them per tile made it the slowest stage.
 #pragma unroll 1
                     for (int rd = 0; rd < K_ROUNDS && ok; rd++) {
-                        ok = mbar_wait_cta(bar(B_KEMPTY + rd), (t & 1) ^ 1, abort_flag, status);
+                        ok = mbar_wait<kSleep>(bar(B_KEMPTY + rd), (t & 1) ^ 1, abort_flag, status);
                         if (!ok) break;
-                        TR_EV(rd);
 #pragma unroll 1
                         for (int c = N_QK * rd; c < min(N_QK * (rd + 1), NSUB); c++) {
                             if (rank == 0) mbar_expect_tx(bar(B_KFULL + c), 2 * SUB_BYTES);
@@ -464,9 +255,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     for (uint32_t pg = 0; pg < uint32_t(PAGES) && ok; pg++) {     // both chunk issuers release a page together
                         uint32_t page = page_of(tbl, s, j, pg);
                         if (page >= n_pages) page = 0;           // flagged by the K producer
-                        ok = mbar_wait_cta(bar(B_VEMPTY + pg), (t & 1) ^ 1, abort_flag, status);
+                        ok = mbar_wait<kSleep>(bar(B_VEMPTY + pg), (t & 1) ^ 1, abort_flag, status);
                         if (!ok) break;
-                        TR_EV(3 + pg);
 #pragma unroll 1
                         for (uint32_t ch = 0; ch < 2; ch++) {
                             const uint32_t v = 2 * pg + ch;
@@ -491,28 +281,19 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             const uint32_t pv_a = desc_lo(sV, SUB_BYTES), pv_b = desc_lo(sP, 16);
             uint32_t t = 0, nseg = 0;
             bool ok = true;
-            TR_DECL(tr_a = 0, tr_b = 0, tr_i = 0, c0 = 0, c1 = 0, c2 = 0, tr_start = clock64());
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
                 const SegInfo s = load_seg(m, seg);
                 if (s.n_tiles == 0) continue;
-                if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
+                if (is_qk) ok = mbar_wait<kSleepCluster>(bar(B_QFULL), nseg & 1, abort_flag, status);
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
                     if (is_qk) {
                         // sub-tiles part, part+4 (, part+8): partial scores into this warp's own 64 columns
-                        TR_NOW(c0);
-                        ok = mbar_wait(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
-                        TR_NOW(c1);
-                        TR_ADD(tr_a, c0, c1);
-                        if (part == 0 && lane == 0) TR_EV(7);
+                        ok = mbar_wait<kSleepCluster>(bar(B_SEMPTY), (t & 1) ^ 1, abort_flag, status);
                         if (!ok) break;
                         const uint32_t d = tmem + COL_S + part * (TILE / 2);
 #pragma unroll 1
                         for (uint32_t c = part; c < uint32_t(NSUB); c += N_QK) {
-                            TR_NOW(c0);
-                            ok = mbar_wait(bar(B_KFULL + c), t & 1, abort_flag, status);
-                            TR_NOW(c1);
-                            TR_ADD(tr_b, c0, c1);
-                            if (part == 0 && lane == 0) TR_EV(8 + c / 4);
+                            ok = mbar_wait<kSleepCluster>(bar(B_KFULL + c), t & 1, abort_flag, status);
                             if (!ok) break;
                             tc_fence_after();
                             if (elect_one()) {
@@ -527,25 +308,14 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                                 }
                             }
                             __syncwarp();
-                            TR_NOW(c2);
-                            TR_ADD(tr_i, c1, c2);
-                            if (part == 0 && lane == 0) TR_EV(26 + c / 4);
                         }
                     } else {
                         // chunk `part` of O^T += V^T P^T over the tile's two pages
-                        TR_NOW(c0);
-                        ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
-                        TR_NOW(c1);
-                        TR_ADD(tr_a, c0, c1);
-                        if (part == 0 && lane == 0) TR_EV(12);
+                        ok = mbar_wait<kSleepCluster>(bar(B_PFULL), t & 1, abort_flag, status);
 #pragma unroll 1
                         for (uint32_t pg = 0; pg < uint32_t(PAGES) && ok; pg++) {
                             const uint32_t v = 2 * pg + part;
-                            TR_NOW(c0);
-                            ok = mbar_wait(bar(B_VFULL + v), t & 1, abort_flag, status);
-                            TR_NOW(c1);
-                            TR_ADD(tr_b, c0, c1);
-                            if (part == 0 && lane == 0) TR_EV(13 + pg);
+                            ok = mbar_wait<kSleepCluster>(bar(B_VFULL + v), t & 1, abort_flag, status);
                             if (!ok) break;
                             tc_fence_after();
                             const uint32_t fresh = (j == 0 && pg == 0) ? 0u : 1u;
@@ -561,19 +331,11 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                                 }
                             }
                             __syncwarp();
-                            TR_NOW(c2);
-                            TR_ADD(tr_i, c1, c2);
-                            if (part == 0 && lane == 0) TR_EV(29 + pg);
                         }
                     }
                 }
                 nseg++;
             }
-#ifdef MLA_TC5_TRACE
-            if (blockIdx.x == 6 && blockIdx.y == 0 && lane == 0 && (part == 0))
-                printf("[%s issuer] tiles %u total %lld wait_%s %lld wait_%s %lld issue %lld\n", is_qk ? "qk" : "pv", t,
-                       clock64() - tr_start, is_qk ? "sempty" : "pfull", tr_a, is_qk ? "kfull" : "vfull", tr_b, tr_i);
-#endif
         }
     } else {
         // ===================== softmax / correction / epilogue (both blocks, 8 warps) =====================
@@ -599,11 +361,11 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         uint32_t t = 0, nseg = 0, nb[2] = {0, 0};             // nb: uses of SYNCB[par] so far
         bool fail = false;
         auto wait_w = [&](uint32_t b, uint32_t parity) {              // completion of tensor-core / TMA work
-            if (!fail) fail = !mbar_wait_cta(b, parity, abort_flag, status);
+            if (!fail) fail = !mbar_wait<kSleep>(b, parity, abort_flag, status);
             fail = __any_sync(0xffffffffu, fail);
         };
         auto wait_x = [&](uint32_t b, uint32_t parity) {              // rounds that carry the twin's DSMEM writes
-            if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
+            if (!fail) fail = !mbar_wait<kSleepCluster>(b, parity, abort_flag, status);
             fail = __any_sync(0xffffffffu, fail);
         };
         auto group_or = [&](bool pred) -> bool {              // barrier over this block's softmax threads + OR
@@ -617,13 +379,6 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             return r != 0;
         };
         bool stop = false;
-        TR_DECL(tr_sfull = 0, tr_ld = 0, tr_exp = 0, tr_synca = 0, tr_slow = 0, tr_pempty = 0, tr_pw = 0, c0 = 0, c1 = 0, c2 = 0,
-                c3 = 0, c4 = 0, c5 = 0, c6 = 0, c7 = 0, tr_start = clock64(), tr_epi = 0);
-        [[maybe_unused]] uint32_t n_slow = 0;
-#ifdef MLA_TC5_TRACE
-        unsigned long long gt0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
-#endif
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
             const SegInfo s = load_seg(m, seg);
             if (s.n_tiles == 0) {
@@ -641,11 +396,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             l_part = 0.0f;
             for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                 const uint32_t par = t & 1;
-                TR_NOW(c0);
                 wait_w(bar(B_SFULL), t & 1);
-                TR_NOW(c1);
-                TR_ADD(tr_sfull, c0, c1);
-                if (st_id == 0) TR_EV(16);
                 uint32_t sv[32];
                 if (!fail) {
                     tc_fence_after();
@@ -668,16 +419,13 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {                       // orders only TMEM reads: no memory release needed
-                        if (rank == 0) mbar_arrive_cta(bar(B_SEMPTY));
+                        if (rank == 0) mbar_arrive(bar(B_SEMPTY));
                         else mbar_arrive_cluster_relaxed(r_sempty);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i++) sv[i] = 0u;
                 }
-                TR_NOW(c2);
-                TR_ADD(tr_ld, c1, c2);
-                if (st_id == 0) TR_EV(17);
                 // Scores stay unscaled in registers: the scale rides in the FMA in front of each exponential, and
                 // the mask pass runs only on a segment's last, partly filled tile.
                 const uint32_t valid = min(uint32_t(TILE), s.n_tok - j * TILE);
@@ -697,10 +445,10 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     if (warp_need) {
                         atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
                         asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
-                        mbar_arrive_local(bar(B_SYNCA0 + par));
+                        mbar_arrive_local_release_cluster(bar(B_SYNCA0 + par));
                         mbar_arrive_cluster(r_synca[par]);
                     } else {
-                        mbar_arrive_cta(bar(B_SYNCA0 + par));
+                        mbar_arrive(bar(B_SYNCA0 + par));
                         mbar_arrive_cluster_relaxed(r_synca[par]);
                     }
                 }
@@ -715,14 +463,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     sum += p0 + p1;
                     pk[i / 2] = Elem<T>::pack2(p0, p1);
                 }
-                TR_NOW(c3);
-                TR_ADD(tr_exp, c2, c3);
-                if (st_id == 0) TR_EV(18);
                 wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
                 if (group_or(fail)) { stop = true; break; }
-                TR_NOW(c4);
-                TR_ADD(tr_synca, c3, c4);
-                if (st_id == 0) TR_EV(19);
                 const bool slow = need_flag[par] != 0;
                 if (slow) {
                     // exchange the token quarters' maxima inside the block, decide per head, publish the
@@ -740,7 +482,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     }
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive_local(bar(B_SYNCB0 + par));
+                        mbar_arrive_local_release_cluster(bar(B_SYNCB0 + par));
                         mbar_arrive_cluster(r_syncb[par]);
                     }
                     wait_x(bar(B_SYNCB0 + par), nb[par] & 1);
@@ -757,12 +499,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 }
                 l_part += sum;
                 // PV of the previous tile must be complete: O is stable and P is free
-                TR_NOW(c5);
-                TR_ADD(tr_slow, c4, c5);
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
-                TR_NOW(c6);
-                TR_ADD(tr_pempty, c5, c6);
-                if (st_id == 0) TR_EV(20);
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
                 if (slow && j > 0) {
@@ -793,20 +530,15 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    if (rank == 0) mbar_arrive_cta(bar(B_PFULL));
+                    if (rank == 0) mbar_arrive(bar(B_PFULL));
                     else mbar_arrive_remote(r_pfull);
                 }
                 // the flag of this parity is next written two tiles from now: clear it once every
                 // thread of the block has read it (they all passed the barrier of the slow path)
                 if (st_id == 0 && slow) need_flag[par] = 0;
-                TR_NOW(c7);
-                TR_ADD(tr_pw, c6, c7);
-                if (st_id == 0) TR_EV(21);
-                if (slow) n_slow++;
             }
             if (stop) break;
             // ---- epilogue: O^T (this block's 256 dims x 128 heads) -> acc[head][dim]; (m, l) of own heads
-            TR_NOW(c0);
             wait_w(bar(B_OFULL), nseg & 1);
             group_or(false);                   // the maxima scratch is free: its bytes now carry the partial sums
             if (tq != 0) l_other[(tq - 1) * HG + hl] = l_part;
@@ -832,18 +564,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             tc_fence_before();
             group_or(false);                   // the scratch is reused by the next segment
             nseg++;
-            TR_NOW(c1);
-            TR_ADD(tr_epi, c0, c1);
         }
-#ifdef MLA_TC5_TRACE
-        unsigned long long gt1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
-        if (blockIdx.x == 6 && blockIdx.y == 0 && st_id == 0)
-            printf("[clock] %lld cycles in %llu ns = %.3f GHz\n", clock64() - tr_start, gt1 - gt0, double(clock64() - tr_start) / double(gt1 - gt0));
-        if (blockIdx.x == 6 && blockIdx.y == 0 && st_id == 0)
-            printf("[softmax] tiles %u slow %u segs %u total %lld: sfull %lld ld %lld exp %lld synca %lld slowpath %lld pempty %lld pwrite %lld epilogue %lld\n",
-                   t, n_slow, nseg, clock64() - tr_start, tr_sfull, tr_ld, tr_exp, tr_synca, tr_slow, tr_pempty, tr_pw, tr_epi);
-#endif
     }
 
     // Neither block may leave while its twin can still signal its barriers, write its scratch or
@@ -851,18 +572,6 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     tc_fence_before();
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-#ifdef MLA_TC5_TRACE
-    if (blockIdx.x == 6 && blockIdx.y == 0 && tid == 0) {
-        const char* names[32] = {"K round0", "K round1", "K round2", "V page0", "V page1", "-", "-", "QK sempty", "QK kfull0",
-                                 "QK kfull4", "QK kfull8", "K5 expected", "PV pfull", "PV vfull0", "PV vfull2", "K5 issued", "SM sfull", "SM ld", "SM exp",
-                                 "SM synca", "SM pempty", "SM pfull", "K0 wait", "K5 waited", "K2 issue", "K3 issue", "QK done0", "QK done4",
-                                 "QK done8", "PV done0", "PV done1", "K5 begin"};
-        const long long o = tr_buf[16];
-        for (int tt = 0; tt < 3; tt++)
-            for (int i = 0; i < 32; i++)
-                if (names[i][0] != '-') printf("EV t=%d %-10s %lld\n", MLA_TR_T0 + tt, names[i], tr_buf[tt * 32 + i] - o);
-    }
-#endif
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -886,8 +595,8 @@ int decode_tc5_pair128_configure()
     return int(e);
 }
 
-// tmaps: [0] pool, box 64 values x 64 tokens (one K sub-tile); [4] pool whole-row view, box 64 tokens x 2 chunks (V);
-// [5] absorbed queries, box 64 rows x 9 chunks.  layer_pool: the layer's slice of the cache pool (linear L2 prefetch).
+// tmaps: the context's tensor-map array (kMapPoolSub = one K sub-tile, kMapPoolV = V boxes, kMapQueries = Q').
+// layer_pool: the layer's slice of the cache pool (linear L2 prefetch).
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
                               const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
 {
@@ -896,10 +605,10 @@ int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_po
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
-        return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4], maps[5],
+        return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV], maps[kMapQueries],
                               static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, status));
-    return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[0], maps[4],
-                          maps[5], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, status));
+    return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV],
+                          maps[kMapQueries], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, status));
 }
 
 }  // namespace mla

@@ -442,18 +442,21 @@ merge_outproj_mma_kernel(const float* __restrict__ recs, const uint32_t* __restr
     }
 }
 
+// Once per device, with that device current (function attributes are per device).
+int merge_mma_configure()
+{
+    cudaError_t e = cudaFuncSetAttribute(merge_outproj_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(merge_outproj_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
+    return int(e);
+}
+
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
                   cudaStream_t st)
 {
     if (rows == 0) return;
     if (!exported) {
-        static bool configured = false;
-        if (!configured) {
-            cudaFuncSetAttribute(merge_outproj_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
-            cudaFuncSetAttribute(merge_outproj_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMergeSmem));
-            configured = true;
-        }
         const uint32_t row_tiles = (rows + 15) / 16;
         dim3 grid16(H, (row_tiles + kMergeTilesPerBlock - 1) / kMergeTilesPerBlock);
         if (dtype == 0)

@@ -21,21 +21,27 @@ void launch_absorb(int dtype, const void* q, const void* w_uk_t, void* q_abs, ui
 // Returns a cudaError_t-compatible code from the launch configuration.
 int launch_decode_mma(int dtype, const void* q_abs, const void* layer_pool, uint32_t n_pages,
                       const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
+int decode_mma_configure();   // the *_configure() functions set kernel attributes on the CURRENT device: once per device
 
 // Split-KV attention on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM,
-// cache tiles staged by TMA): grid (persistent blocks, ceil(H/64)).  tmaps points at two host
-// CUtensorMap objects: [0] the whole pool ([layers][slots][576]), [1] the absorbed queries.
-int launch_decode_tc5(int dtype, const void* q_abs, const void* tmaps, uint32_t layer,
-                      uint32_t n_pages, const StepMeta& m, float* recs, uint32_t H, uint32_t* status,
-                      cudaStream_t st);
-int decode_tc5_configure();   // sets the kernel's shared-memory attribute once
+// cache tiles staged by TMA): grid (persistent blocks, ceil(H/64)).  tmaps points at the context's
+// host CUtensorMap array (kMap* below); this kernel uses kMapPoolPage and kMapQueries.
+int launch_decode_tc5(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
+                      float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
+int decode_tc5_configure();   // sets the kernel's attributes on the current device
 
-// The same on a pair of SMs (cluster of 2, tcgen05.mma.cta_group::2): grid (2 x persistent pairs,
-// ceil(H/128)).  tmaps: [1] absorbed queries, [2] the pool with a 32-token box.
-int launch_decode_tc5_pair(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m,
-                           float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
-int decode_tc5_pair_configure();
-// same contract, 128-token tiles (two pages per score MMA series); uses tmaps [0], [4], [5] and the layer's pool slice
+// Tensor maps a context builds once (mla_api.cu, make_tensor_maps), by index into its array.
+enum : int {
+    kMapPoolSub = 0,      // cache pool [layers][slots][576]: box 64 values x 64 tokens (one K sub-tile)
+    kMapPoolV = 1,        // cache pool, whole-row view (64 values, slots, 9 chunks, layers): box 64 tokens x 2 chunks
+    kMapQueries = 2,      // absorbed queries, whole-row view: box 64 head rows x 9 chunks
+    kMapPoolPage = 3,     // cache pool, whole-row view: box 64 tokens x 9 chunks (one page in one instruction)
+    kMapCount = 4
+};
+
+// The same on a pair of SMs (cluster of 2, tcgen05.mma.cta_group::2), 128-token tiles (two pages per score
+// MMA series): grid (2 x persistent pairs, ceil(H/128)).  Uses kMapPoolSub, kMapPoolV, kMapQueries and the
+// layer's pool slice.
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
                               const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
 int decode_tc5_pair128_configure();
@@ -43,6 +49,7 @@ int decode_tc5_pair128_configure();
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
                   cudaStream_t st);
+int merge_mma_configure();
 
 // Absorb on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the layer's W_UK^T,
 // [H*512 d][128 i], box 64 i x 256 d, 128-byte swizzle.  With kv_a != nullptr the same launch appends the step's

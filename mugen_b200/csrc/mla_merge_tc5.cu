@@ -16,19 +16,14 @@
 // The mma.sync version of this step (merge_outproj_mma_kernel) re-reads the operands from shared
 // memory once per warp and spends ~40 us per layer at batch 64; here every operand byte is read
 // once by the tensor core.
-#include <cuda.h>
-#ifdef MLA_TC5_TRACE
-#include <cstdio>
-#define MTR(i) do { if (tid == 0 && blockIdx.x == 5) mtr[i] = clock64(); } while (0)
-#else
-#define MTR(i)
-#endif
-
 #include "mla_launch.h"
+#include "mla_tc5.cuh"
 
 namespace mla {
 
 namespace {
+
+using namespace tc5;
 
 constexpr int MT = 64;                         // query rows per block
 constexpr int W_SUB = kVDim * 128;             // 16,384: [128 outputs][64 dims]
@@ -46,88 +41,7 @@ constexpr int MISC_BYTES = 64;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // + slack to round the base up to 1 KB
 constexpr int NUM_THREADS = 512;
 constexpr uint32_t TMEM_COLS = 128;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded: gives up after about two seconds, raises the status bit and tells the block through `fail_flag`
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* fail_flag, uint32_t* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*fail_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *fail_flag = 1;
-                atomicOr(status, ST_WAIT_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n.reg .pred px;\nelect.sync _|px, 0xFFFFFFFF;\n@px mov.s32 %0, 1;\n}\n" : "+r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "setp.ne.b32 p, %6, 0;\n"
-        "mov.b64 da, {%1, %2};\n"
-        "mov.b64 db, {%3, %4};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// shared-memory matrix descriptor halves (K-major, 128-byte swizzle, 8-row groups 1 KB apart)
-__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
-constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m, uint32_t n) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 
 template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -151,10 +65,6 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
         return recs + idx * kPart;
     };
 
-#ifdef MLA_TC5_TRACE
-    long long mtr[12] = {0};
-#endif
-    MTR(0);
     grid_launch_dependents();
     if (tid == 0) {
         *fail_flag = 0;
@@ -172,8 +82,6 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    MTR(1);
-    MTR(2);
 
     if (tid == 0) {                                       // W_UV_h: eight boxes of 64 dims x 128 outputs
         mbar_expect_tx(bar_w, W_BYTES);
@@ -259,10 +167,8 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
                     p[x] += 4;
                 }
             }
-            MTR(3 + 4 * kh);
             // the first half's MMAs read the operand buffers until they complete
             if (kh == 1 && pr == 0) ok = mbar_wait(bar_mma, 0, fail_flag, status);
-            MTR(4 + 4 * kh);
 #pragma unroll
             for (int x = 0; x < 2; x++) {
                 const float inv = L[x] > 0.0f ? 1.0f / L[x] : 0.0f;
@@ -281,7 +187,6 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         tc_fence_before();
         __syncthreads();
-        MTR(5 + 4 * kh);
         if (warp == 0) {
             if (kh == 0) ok = mbar_wait(bar_w, 0, fail_flag, status) && ok;
             tc_fence_after();
@@ -291,23 +196,21 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const uint32_t b = desc_lo(sW + (kh * 4 + s) * W_SUB + k * 32);
-                        tc_mma(tmem, desc_lo(sAhi + s * A_SUB + k * 32), DESC_HI, b, DESC_HI, IDESC,
+                        tc_mma(tmem, desc_lo(sAhi + s * A_SUB + k * 32), desc_hi(1024), b, desc_hi(1024), IDESC,
                                (kh == 0 && s == 0 && k == 0) ? 0u : 1u);
-                        tc_mma(tmem, desc_lo(sAlo + s * A_SUB + k * 32), DESC_HI, b, DESC_HI, IDESC, 1u);
+                        tc_mma(tmem, desc_lo(sAlo + s * A_SUB + k * 32), desc_hi(1024), b, desc_hi(1024), IDESC, 1u);
                     }
                 }
                 tc_commit(bar_mma);
             }
             __syncwarp();
         }
-        MTR(6 + 4 * kh);
     }
 
     if (warp < 4) {
         // D (M=64): rows 16*warp .. 16*warp+15 sit in lanes 0-15 of the warp's TMEM sub-partition
         ok = mbar_wait(bar_mma, 1, fail_flag, status) && ok;
         ok = __all_sync(0xffffffffu, ok);
-        MTR(11);
         if (ok) {
             tc_fence_after();
             const uint32_t row = r0 + 16 * warp + lane;
@@ -332,14 +235,6 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     }
     tc_fence_before();
     __syncthreads();
-#ifdef MLA_TC5_TRACE
-    if (tid == 0 && blockIdx.x == 5) {
-        const long long e = clock64();
-        printf("[merge] prologue %lld phase1 %lld | h0: reduce %lld wait %lld write+sync %lld issue %lld | h1: reduce %lld wait %lld write+sync %lld issue %lld | mma wait %lld epilogue %lld\n",
-               mtr[1] - mtr[0], mtr[2] - mtr[1], mtr[3] - mtr[2], mtr[4] - mtr[3], mtr[5] - mtr[4], mtr[6] - mtr[5], mtr[7] - mtr[6],
-               mtr[8] - mtr[7], mtr[9] - mtr[8], mtr[10] - mtr[9], mtr[11] - mtr[10], e - mtr[11]);
-    }
-#endif
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");

@@ -31,7 +31,16 @@ constexpr size_t kQAbsBytes = size_t(kMaxHeads) * mla::kRow * 2;
 constexpr size_t kRecBytes = size_t(kMaxSegs) * kMaxHeads * mla::kPart * sizeof(float);
 constexpr size_t kOffQAbs = kMetaBytes;
 constexpr size_t kOffRecs = kOffQAbs + ((kQAbsBytes + 255) & ~size_t(255));
-constexpr size_t kScratchBytes = kOffRecs + kRecBytes;    // 8,581,120 B, about 8.2 MiB
+constexpr size_t kScratchBytes = kOffRecs + kRecBytes;    // 8,577,024 B, about 8.2 MiB
+static_assert(kScratchBytes == 8577024, "the size quoted in the public header");
+
+// The call's bookkeeping at the start of the scratch array, in the form the attention kernels read.
+struct Meta {
+    uint32_t row_seq, row_len, tbl_off, row_seg_begin[2];
+    uint32_t seg_row[kMaxSegs], seg_pb[kMaxSegs], seg_pe[kMaxSegs];
+    uint32_t table[kMaxSeqLen / mla::kPage];
+};
+static_assert(sizeof(Meta) <= kMetaBytes - 4, "metadata region too small (its last word is the status word)");
 
 // In host code this name is only a stand-in for the symbol, not a device address: the address a
 // kernel can use comes from cudaGetSymbolAddress (see scratch_for_current_device).
@@ -67,7 +76,32 @@ absorb_one_row_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, T* __
     *reinterpret_cast<uint32_t*>(q_abs + size_t(h) * mla::kRow + tid * 2) = mla::Elem<T>::pack2(a0, a1);
 }
 
-// Device address of the scratch array on the CURRENT device, resolved once per device.
+// The split-KV plan (equal page ranges), the identity block table of the contiguous cache and a cleared
+// status word, written by the device itself: the host passes two integers, so a call copies nothing from
+// host memory.
+__global__ void __launch_bounds__(256)
+noalloc_plan_kernel(unsigned char* scratch, uint32_t seq_len, uint32_t pages, uint32_t segs)
+{
+    Meta* mt = reinterpret_cast<Meta*>(scratch);
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) {
+        mt->row_seq = 0;
+        mt->row_len = seq_len;
+        mt->tbl_off = 0;
+        mt->row_seg_begin[0] = 0;
+        mt->row_seg_begin[1] = segs;
+        *reinterpret_cast<uint32_t*>(scratch + kMetaBytes - 4) = 0;
+    }
+    if (tid < segs) {
+        mt->seg_row[tid] = 0;
+        mt->seg_pb[tid] = uint32_t(uint64_t(pages) * tid / segs);
+        mt->seg_pe[tid] = uint32_t(uint64_t(pages) * (tid + 1) / segs);
+    }
+    for (uint32_t p = tid; p < pages; p += blockDim.x) mt->table[p] = p;
+}
+
+// Device address of the scratch array on the CURRENT device.  The first call on a device resolves it and
+// sets the two kernels' shared-memory attributes there (both are per-device state).
 int scratch_for_current_device(unsigned char** out)
 {
     static unsigned char* ptrs[64] = {};
@@ -80,6 +114,10 @@ int scratch_for_current_device(unsigned char** out)
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || !p)
             return fail(MLA_ERR_CUDA, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+        if (int ce = mla::decode_mma_configure())
+            return fail(MLA_ERR_CUDA, std::string("attention kernel attributes: ") + cudaGetErrorString(cudaError_t(ce)));
+        if (int ce = mla::merge_mma_configure())
+            return fail(MLA_ERR_CUDA, std::string("merge kernel attributes: ") + cudaGetErrorString(cudaError_t(ce)));
         ptrs[dev] = static_cast<unsigned char*>(p);
     }
     *out = ptrs[dev];
@@ -107,29 +145,12 @@ int mla_attention_noalloc(uint32_t dtype, uint32_t n_heads, uint32_t seq_len, co
     unsigned char* scratch = nullptr;
     if (int rc = scratch_for_current_device(&scratch)) return rc;
 
-    // ---- segment plan and identity block table, built on the stack and copied into the scratch
+    // ---- segment plan, identity block table and status word: written on the device
     const uint32_t pages = (seq_len + mla::kPage - 1) / mla::kPage;
     const uint32_t segs = pages == 0 ? 1 : (pages < kMaxSegs ? pages : kMaxSegs);
-    struct Meta {
-        uint32_t row_seq, row_len, tbl_off, row_seg_begin[2];
-        uint32_t seg_row[kMaxSegs], seg_pb[kMaxSegs], seg_pe[kMaxSegs];
-        uint32_t table[kMaxSeqLen / mla::kPage];
-    } mt;
-    static_assert(sizeof(Meta) <= kMetaBytes, "metadata region too small");
-    mt.row_seq = 0;
-    mt.row_len = seq_len;
-    mt.tbl_off = 0;
-    mt.row_seg_begin[0] = 0;
-    mt.row_seg_begin[1] = segs;
-    for (uint32_t g = 0; g < segs; g++) {
-        mt.seg_row[g] = 0;
-        mt.seg_pb[g] = uint32_t(uint64_t(pages) * g / segs);
-        mt.seg_pe[g] = uint32_t(uint64_t(pages) * (g + 1) / segs);
-    }
-    for (uint32_t p = 0; p < pages; p++) mt.table[p] = p;
-    const size_t meta_used = offsetof(Meta, table) + size_t(pages) * 4;
-    cudaError_t e = cudaMemcpyAsync(scratch, &mt, meta_used, cudaMemcpyHostToDevice, st);   // pageable source: staged before return
-    if (e != cudaSuccess) return fail(MLA_ERR_CUDA, std::string("metadata copy: ") + cudaGetErrorString(e));
+    noalloc_plan_kernel<<<1, 256, 0, st>>>(scratch, seq_len, pages, segs);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MLA_ERR_CUDA, std::string("plan launch: ") + cudaGetErrorString(e));
 
     mla::StepMeta m{};
     auto at = [&](size_t off) { return reinterpret_cast<const uint32_t*>(scratch + off); };
@@ -150,9 +171,9 @@ int mla_attention_noalloc(uint32_t dtype, uint32_t n_heads, uint32_t seq_len, co
 
     void* q_abs = scratch + kOffQAbs;
     float* recs = reinterpret_cast<float*>(scratch + kOffRecs);
+    // The kernels want a status word to report into; this path has no call that reads it back (the only bit
+    // they can raise here, a bad page id, cannot occur with the identity table built above).
     uint32_t* status = reinterpret_cast<uint32_t*>(scratch + kMetaBytes - 4);   // last word of the metadata region
-    e = cudaMemsetAsync(status, 0, 4, st);
-    if (e != cudaSuccess) return fail(MLA_ERR_CUDA, std::string("status clear: ") + cudaGetErrorString(e));
     if (dtype == MLA_DTYPE_F16)
         absorb_one_row_kernel<__half><<<n_heads, 256, 0, st>>>(static_cast<const __half*>(q), static_cast<const __half*>(w_uk),
                                                                static_cast<__half*>(q_abs));

@@ -36,8 +36,10 @@ def _both_ways(torch, seed, n_heads, seq_len, dt):
     ctx.attend_rows(0, [s], [seq_len], _dev(torch, case.q), want)
     torch.cuda.synchronize()
     ctx.close()
-    # the caller's own buffers: a contiguous cache padded to a multiple of 64 finite rows
-    padded = np.zeros(((seq_len + 63) // 64 * 64, 576), np.uint16)
+    # the caller's own buffers: a contiguous cache of exactly seq_len rows.  The allocation continues with
+    # rows of NaN bit patterns: the entry point promises to read nothing behind the last row, and if it did
+    # and multiplied them by a zero probability, the NaNs would show in the output.
+    padded = np.full((seq_len + 64, 576), 0x7FC0 if dt == synth.DT_BF16 else 0x7E00, np.uint16)
     padded[:seq_len] = case.caches[0]
     d_cache, d_q = _dev(torch, padded), _dev(torch, case.q[0])
     d_wk, d_wv = _dev(torch, case.w_uk), _dev(torch, case.w_uv)
