@@ -129,7 +129,24 @@ class _Reference:
         for f in ("ref_ggml_f16", "ref_ggml_q8_0", "ref_ggml_q4_0"):
             getattr(L, f).restype = _u32
         assert (L.ref_ggml_f16(), L.ref_ggml_q4_0(), L.ref_ggml_q8_0()) == (W_F16, W_Q4_0, W_Q8_0)
+        L.ref_model_load.restype = _vp
+        L.ref_model_load.argtypes = [C.c_char_p]
+        L.ref_model_free.argtypes = [_vp]
+        L.ref_model_last_error.restype = C.c_char_p
+        L.ref_model_config.argtypes = [_vp, _vp, _vp]
+        L.ref_model_weight.restype = _u32
+        L.ref_model_weight.argtypes = [_vp, _u32, _u32, _vp, C.c_size_t]
+        L.ref_model_forward.restype = C.c_int
+        L.ref_model_forward.argtypes = [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]
+        L.ref_model_cache_rows.argtypes = [_vp, _u32, _u32, _u32, _vp]
+        L.ref_model_seq_len.restype = _u32
+        L.ref_model_seq_len.argtypes = [_vp]
+        L.ref_model_truncate.argtypes = [_vp, _u32]
         self.L = L
+
+    def load_model(self, gguf_path: str) -> "_RefModel":
+        """The reference's from_gguf on a GGUF file (see _RefModel)."""
+        return _RefModel(self.L, gguf_path)
 
     def yarn_rope_freq(self, pair, rope_dim, factor, orig_ctx, theta) -> np.float32:
         return np.float32(self.L.ref_yarn_rope_freq(pair, rope_dim, factor, orig_ctx, theta))
@@ -148,6 +165,57 @@ class _Reference:
         self.L.ref_mla_attention_batch(_ptr(q), ptrs, _ptr(lens), n, _ptr(w_uk), _ptr(w_uv),
                                        w_type, n_heads, _ptr(out), n_threads)
         return out
+
+
+class _RefModel:
+    """The reference's TransformerModel built by its own from_gguf from a GGUF file, driven through its own
+    forward() on host stand-ins of the Metal layer (oracle/ref_harness.cpp).  forward() returns what the
+    decode driver's host code read and wrote per layer."""
+    WEIGHTS = dict(w_uk=0, w_uv=1, kv_a_norm=2, kv_a_mqa=3, q_a=4, q_a_norm=5, q_b=6, q=7, wo=8, attn_norm=9)
+
+    def __init__(self, L, path: str) -> None:
+        self.L = L
+        self.h = L.ref_model_load(path.encode())
+        if not self.h:
+            raise RuntimeError(L.ref_model_last_error().decode())
+        cfg = np.zeros(12, np.uint32)
+        fcfg = np.zeros(3, np.float32)
+        L.ref_model_config(self.h, _ptr(cfg), _ptr(fcfg))
+        names = ["n_layers", "n_heads", "embed", "kv_lora_rank", "q_lora_rank", "qk_nope", "qk_rope", "v_head_dim",
+                 "rope_original_ctx", "max_seq_len", "vocab", "ffn"]
+        self.cfg = {k: int(v) for k, v in zip(names, cfg)}
+        self.cfg.update(rope_theta=float(fcfg[0]), rope_scaling_factor=float(fcfg[1]), rms_norm_eps=float(fcfg[2]))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.ref_model_free(self.h)
+            self.h = None
+
+    def weight(self, layer: int, which: str, n_bytes: int):
+        """(GGML type, raw bytes) of a layer's weight as the loaded model holds it, or None when absent."""
+        buf = np.zeros(n_bytes, np.uint8)
+        t = self.L.ref_model_weight(self.h, layer, self.WEIGHTS[which], _ptr(buf), n_bytes)
+        return None if t == 0xFFFFFFFF else (int(t), buf)
+
+    def forward(self, token: int, pos: int) -> dict:
+        c = self.cfg
+        Lr, H, E = c["n_layers"], c["n_heads"], c["embed"]
+        t = dict(hidden_in=np.zeros((Lr, E), np.uint16), q_pre=np.zeros((Lr, H, QDIM), np.uint16),
+                 q_post=np.zeros((Lr, H, QDIM), np.uint16), kv_a_pre=np.zeros((Lr, ROW), np.uint16),
+                 attn_out=np.zeros((Lr, H, VDIM), np.uint16), hidden_mid=np.zeros((Lr, E), np.uint16))
+        rc = self.L.ref_model_forward(self.h, token, pos, _ptr(t["hidden_in"]), _ptr(t["q_pre"]), _ptr(t["q_post"]),
+                                      _ptr(t["kv_a_pre"]), _ptr(t["attn_out"]), _ptr(t["hidden_mid"]))
+        if rc:
+            raise RuntimeError(self.L.ref_model_last_error().decode())
+        return t
+
+    def cache_rows(self, layer: int, row_begin: int, n: int) -> np.ndarray:
+        out = np.zeros((n, ROW), np.uint16)
+        self.L.ref_model_cache_rows(self.h, layer, row_begin, n, _ptr(out))
+        return out
+
+    def seq_len(self) -> int:
+        return int(self.L.ref_model_seq_len(self.h))
 
 
 _oracle: _Oracle | None = None

@@ -5,16 +5,21 @@ oracle/Makefile `ref` and executes them):
 
     python tests/golden/make_golden.py
 
-Attention, YaRN-frequency and KVCache-counter entries are outputs of the REFERENCE's code.
-Append entries come from the restatement in oracle/mla_oracle.cpp (the reference's append
-arithmetic is inline in forward() and not callable); they guard against regressions only.
-Inputs are not stored: each entry carries the generator arguments and a SHA-256 of the
-generated inputs, so a drifting generator is detected instead of silently re-baselined.
+Attention, YaRN-frequency, KVCache-counter, append and q-RoPE entries are outputs of the REFERENCE's
+code.  The append (RMSNorm + NeoX/YaRN RoPE + scatter) and the q RoPE are inline in the reference's forward()
+and not callable, so they are reached by running its real from_gguf + forward() on a tiny synthetic deepseek2
+GGUF file (tests/golden/tiny_gguf.py) over host stand-ins of the Metal layer (oracle/ref_harness.cpp): the
+entries hold what that code read (kv_a, q before rotation) and what it wrote (the cache row, q after rotation).
+"append_restated" entries come from the restatement in oracle/mla_oracle.cpp (bf16 storage and very large
+positions, which the f16-only reference with its [context_length][576] buffers does not offer); they guard
+against regressions only.  Where inputs are not stored, an entry carries the generator arguments and a
+SHA-256 of the generated inputs, so a drifting generator is detected instead of silently re-baselined.
 """
 import base64
 import json
 import os
 import sys
+import tempfile
 
 import numpy as np
 
@@ -23,6 +28,19 @@ sys.path.insert(0, ROOT)
 
 from mugen_b200 import synth  # noqa: E402
 from oracle import binding  # noqa: E402
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import tiny_gguf  # noqa: E402
+
+# Tiny models driven through the reference's forward(); `steps` = (token, position) calls in order, `keep` =
+# the positions whose rows are stored.  The reference writes the row at the caller's position without checking
+# that it equals seq_len (src/core/model/transformer.cpp:3982), so model B may jump.
+FORWARD_CASES = [
+    dict(name="A: q-LoRA, separate k_b/v_b, YaRN factor 40", model=dict(),
+         steps=[(p % 16, p) for p in range(67)], keep=[0, 1, 31, 63, 64, 66]),
+    dict(name="B: full q, merged kv_b, plain RoPE, eps 1e-5",
+         model=dict(q_lora_rank=0, merged_kv_b=True, rope_factor=1.0, eps=1e-5, context_length=8192, seed=11, n_heads=2),
+         steps=[(3, 0), (5, 63), (7, 64), (9, 4095), (11, 8191)], keep=[0, 63, 64, 4095, 8191]),
+]
 
 ATTN_CASES = [
     # seed, heads, seq_len, w_type, q_scale, exact_in_both
@@ -90,12 +108,36 @@ def main() -> None:
     ref.L.ref_kvcache_destroy(kc)
     out["counter"].append({"trace": COUNTER_TRACE, "seq_len_after": lens,
                            "source": "reference KVCache (MLA construction)"})
+    out["append_restated"] = []
     for c in APPEND_CASES:
         case = synth.make_layer_case(c["seed"], 1, [1] * c["n"], c["dt"])
         rows = ora.append_rows(case.kv_a, c["positions"], case.norm_w, c["eps"], c["factor"],
                                c["orig_ctx"], c["theta"], c["dt"])
-        out["append"].append({**c, "inputs_sha256": case.digest(), "rows": b64(rows),
-                              "source": "restatement (oracle/mla_oracle.cpp)"})
+        out["append_restated"].append({**c, "inputs_sha256": case.digest(), "rows": b64(rows),
+                                       "source": "restatement (oracle/mla_oracle.cpp)"})
+    out["q_rope"] = []
+    with tempfile.TemporaryDirectory() as tmp:
+        for fc in FORWARD_CASES:
+            path = os.path.join(tmp, "tiny.gguf")
+            tiny_gguf.write(path, tiny_gguf.TinyModel(**fc["model"]))
+            mod = ref.load_model(path)
+            cfg = mod.cfg
+            common = dict(model=fc["name"], factor=cfg["rope_scaling_factor"], orig_ctx=cfg["rope_original_ctx"],
+                          theta=cfg["rope_theta"], eps=cfg["rms_norm_eps"], dt=synth.DT_F16)
+            norm_w = [mod.weight(L, "kv_a_norm", 1024)[1].view(np.uint16) for L in range(cfg["n_layers"])]
+            for token, pos in fc["steps"]:
+                taps = mod.forward(token, pos)
+                if pos not in fc["keep"]:
+                    continue
+                for L in range(cfg["n_layers"]):
+                    out["append"].append({**common, "layer": L, "position": pos, "kv_a": b64(taps["kv_a_pre"][L]),
+                                          "norm_w": b64(norm_w[L]), "row": b64(mod.cache_rows(L, pos, 1)[0]),
+                                          "source": "reference forward(), steps G+H"})
+                # one layer's q is enough per position (n_heads x 192 values each way)
+                out["q_rope"].append({**common, "position": pos, "n_heads": cfg["n_heads"],
+                                      "q_in": b64(taps["q_pre"][0]), "q_out": b64(taps["q_post"][0]),
+                                      "source": "reference forward(), step E"})
+            mod.close()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mla_golden.json")
     with open(path, "w") as f:
         json.dump(out, f, indent=1)

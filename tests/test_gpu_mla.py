@@ -103,6 +103,39 @@ def test_append_bit_exact(torch, oracle, dt, factor, ctx_len):
     ctx.close()
 
 
+def test_append_reproduces_the_rows_of_the_reference_forward(torch, golden):
+    """Golden rows written by the reference's own inline append (RMSNorm + NeoX/YaRN RoPE + scatter inside
+    forward(), transformer.cpp:3930-3987, run on a tiny deepseek2 GGUF file): the append kernel, fed the kv_a the
+    reference's code read, must store the very bits the reference stored."""
+    import base64
+    from mugen_b200.mla import MlaContext
+    unb = lambda t: np.frombuffer(base64.b64decode(t), np.uint16).copy()
+    groups = {}
+    for c in golden["append"]:
+        groups.setdefault((c["model"], c["layer"]), []).append(c)
+    assert len(groups) >= 4
+    dummy_w = np.zeros((128, 512), np.uint16)
+    for (model, layer), entries in groups.items():
+        c0 = entries[0]
+        assert c0["source"].startswith("reference forward()") and c0["dt"] == synth.DT_F16
+        top = max(c["position"] for c in entries)
+        ctx = MlaContext(n_layers=1, n_heads=1, dtype=synth.DT_F16, n_pages=len(entries) + 1, max_seqs=1,
+                         max_seq_len=64, max_position=top + 1, max_rows=len(entries), kernel=capi.KERNEL_MMA, rope_theta=c0["theta"],
+                         rope_scaling_factor=c0["factor"], rope_original_ctx=c0["orig_ctx"], rms_norm_eps=c0["eps"])
+        ctx.set_layer_weights(0, dummy_w, dummy_w, synth.W_F16, unb(c0["norm_w"]))
+        # one sequence per entry would need a page table per position; instead place each row at its position
+        # modulo the page size (the rotation uses the true position through a base offset)
+        for c in entries:
+            s = ctx.seq_create()
+            ctx.seq_set_base(s, c["position"] - c["position"] % 64)
+            ctx.append_rows(0, [s], [c["position"]], _dev(torch, unb(c["kv_a"])[None]))
+            got = ctx.read_rows(0, s, c["position"] % 64, 1)[0]
+            assert np.array_equal(got, unb(c["row"])), (model, layer, c["position"])
+            ctx.seq_free(s)
+        assert ctx.status() == 0
+        ctx.close()
+
+
 def test_append_many_rows_bit_exact(torch, oracle):
     """A 300-row chunk appended in one call (the batched twin, transformer.cpp:1263-1323)."""
     n = 300

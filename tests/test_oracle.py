@@ -2,6 +2,8 @@
 and (b) that code itself wherever its build is present.  Bit-exact throughout."""
 import base64
 
+import os
+
 import numpy as np
 import pytest
 
@@ -57,7 +59,17 @@ def test_golden_counter_trace(oracle, golden):
 
 
 def test_golden_append_regression(oracle, golden):
+    assert len(golden["append"]) >= 12
     for c in golden["append"]:
+        # inputs and outputs of the reference's own inline append, recorded from its forward()
+        assert c["source"].startswith("reference forward()")
+        got = oracle.append_rows(_unb64(c["kv_a"], np.uint16), [c["position"]], _unb64(c["norm_w"], np.uint16), c["eps"],
+                                 c["factor"], c["orig_ctx"], c["theta"], c["dt"])
+        assert np.array_equal(got[0], _unb64(c["row"], np.uint16)), (c["model"], c["layer"], c["position"])
+    for c in golden["q_rope"]:
+        got = oracle.q_rope(_unb64(c["q_in"], np.uint16), c["position"], c["factor"], c["orig_ctx"], c["theta"], c["dt"])
+        assert np.array_equal(got.reshape(-1), _unb64(c["q_out"], np.uint16)), (c["model"], c["position"])
+    for c in golden["append_restated"]:
         case = synth.make_layer_case(c["seed"], 1, [1] * c["n"], c["dt"])
         assert case.digest() == c["inputs_sha256"]
         got = oracle.append_rows(case.kv_a, c["positions"], case.norm_w, c["eps"], c["factor"],
@@ -144,6 +156,49 @@ def test_restatement_yarn_equals_reference(oracle, reference):
         a = oracle.yarn_rope_freq(i, 64, factor, ctx, theta)
         b = reference.yarn_rope_freq(i, 64, factor, ctx, theta)
         assert a.view(np.uint32) == b.view(np.uint32)
+
+
+@pytest.mark.parametrize("variant", ["lora_yarn", "full_q_merged_kv_b_plain_rope", "q8_0_kv_b"])
+def test_append_and_q_rope_restatements_equal_reference_forward(oracle, reference, tmp_path, variant):
+    """The reference's append (steps G+H) and q RoPE (step E) are inline in forward(): run the real from_gguf +
+    forward() on a tiny synthetic deepseek2 GGUF file and compare, bit for bit, every cache row it writes and
+    every rotated q it hands to the attention with the restatements fed the same kv_a / q."""
+    if reference is None:
+        pytest.skip("reference build not present")
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import tiny_gguf
+    model = {"lora_yarn": dict(seed=21),
+             "full_q_merged_kv_b_plain_rope": dict(seed=22, q_lora_rank=0, merged_kv_b=True, rope_factor=0.5, eps=1e-5,
+                                                   context_length=4096, n_heads=3),
+             "q8_0_kv_b": dict(seed=23, kv_b_type=tiny_gguf.GGML_Q8_0, n_layers=1, rope_factor=4.0, rope_orig_ctx=128)}[variant]
+    path = str(tmp_path / "tiny.gguf")
+    tiny_gguf.write(path, tiny_gguf.TinyModel(**model))
+    mod = reference.load_model(path)
+    c = mod.cfg
+    assert (c["kv_lora_rank"], c["qk_nope"], c["qk_rope"], c["v_head_dim"]) == (512, 128, 64, 128)
+    rope = (c["rope_scaling_factor"], c["rope_original_ctx"], c["rope_theta"])
+    positions = list(range(70)) if variant != "full_q_merged_kv_b_plain_rope" else [0, 1, 63, 64, 65, 1000, 4095]
+    for n, pos in enumerate(positions):
+        taps = mod.forward(n % c["vocab"], pos)
+        for L in range(c["n_layers"]):
+            norm_w = mod.weight(L, "kv_a_norm", 1024)[1].view(np.uint16)
+            want = mod.cache_rows(L, pos, 1)[0]
+            got = oracle.append_rows(taps["kv_a_pre"][L][None], [pos], norm_w, c["rms_norm_eps"], *rope, synth.DT_F16)[0]
+            assert np.array_equal(got, want), (variant, L, pos)
+            q = oracle.q_rope(taps["q_pre"][L], pos, *rope, synth.DT_F16)
+            assert np.array_equal(q.reshape(-1), taps["q_post"][L].reshape(-1)), (variant, L, pos)
+            # the attention the driver ran on its own cache is the routine the other tests pin
+            seq_len = mod.seq_len()          # counter moved once, after all layers
+            if pos + 1 == seq_len:
+                cache = mod.cache_rows(L, 0, seq_len)
+                nb = c["n_heads"] * 128 * 512 * 2 if variant != "q8_0_kv_b" else c["n_heads"] * 128 * 16 * 34
+                wt, w_uk = mod.weight(L, "w_uk", nb)
+                _, w_uv = mod.weight(L, "w_uv", nb)
+                att = oracle.attention(taps["q_post"][L], cache, seq_len, w_uk, w_uv, wt, c["n_heads"], synth.DT_F16)
+                assert np.array_equal(att, taps["attn_out"][L]), (variant, L, pos)
+    assert mod.seq_len() == len(positions)       # advance_seq_len(1) once per token (transformer.cpp:4401-4403)
+    mod.close()
 
 
 def test_quant_pack_roundtrip():
