@@ -221,6 +221,14 @@ int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_be
 int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
                    const void* dev_rows, void* stream);
 
+/* Failure-path self-test (no reference counterpart).  Launches one block whose threads wait on a barrier that
+ * nothing completes: after `limit_cycles` SM cycles (e.g. 1,000,000: about half a millisecond) the wait gives up,
+ * raises the ST_WAIT_TIMEOUT bit (value 4) in the context's device status word, the block frees its tensor memory
+ * and returns.  This is the mechanism every kernel here uses instead of hanging or trapping; a following
+ * mla_status() returns MLA_ERR_DEVICE with device_status = 4 and clears the word, and the context stays usable.
+ * waited_cycles (HOST pointer, may be NULL) receives how long the block waited.  Synchronises the stream. */
+int mla_selftest_wait_timeout(mla_ctx* ctx, uint64_t limit_cycles, void* stream, uint32_t* waited_cycles);
+
 /* ---- for callers that may not allocate ------------------------------------------------------ */
 /* No counterpart in the reference.  Absorbed MLA attention of one query row over one CONTIGUOUS
  * latent cache, without a context and without any allocation: no cudaMalloc, cudaFree or

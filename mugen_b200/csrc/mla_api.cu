@@ -1008,6 +1008,28 @@ int mla_set_q_rope(mla_ctx* c, int in_kernel)
     return MLA_OK;
 }
 
+int mla_selftest_wait_timeout(mla_ctx* c, uint64_t limit_cycles, void* stream, uint32_t* waited_cycles)
+{
+    if (!c) return MLA_ERR_INVALID;
+    USE_DEVICE(c);
+    if (limit_cycles == 0 || limit_cycles > 2000000000ull)
+        return fail(c, MLA_ERR_INVALID, "limit_cycles must be in 1 .. 2e9 (about a second)");
+    auto st = static_cast<cudaStream_t>(stream);
+    uint32_t* report = nullptr;
+    CU_TRY(c, cudaMalloc(&report, 8));
+    mla::launch_wait_timeout_selftest(static_cast<long long>(limit_cycles), c->status_dev, report, st);
+    c->launches++;
+    uint32_t host[2] = {1, 0};
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host, report, 8, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(report);
+    if (e != cudaSuccess) return fail(c, MLA_ERR_CUDA, std::string("wait-timeout self-test: ") + cudaGetErrorString(e));
+    if (waited_cycles) *waited_cycles = host[1];
+    if (host[0] != 0) return fail(c, MLA_ERR_DEVICE, "the self-test's wait did not give up");
+    return MLA_OK;
+}
+
 int mla_profile_enable(mla_ctx* c, int on)
 {
     if (!c) return MLA_ERR_INVALID;

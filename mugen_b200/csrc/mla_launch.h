@@ -66,4 +66,8 @@ int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin
                      void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st);
 int merge_tc5_configure();
 
+// One block that waits `limit_cycles` on a barrier nothing completes, raises ST_WAIT_TIMEOUT in *status, frees its
+// tensor memory and returns; report[0] = 0 when the wait gave up, report[1] = cycles waited.
+void launch_wait_timeout_selftest(long long limit_cycles, uint32_t* status, uint32_t* report, cudaStream_t st);
+
 }  // namespace mla

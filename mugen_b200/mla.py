@@ -200,6 +200,12 @@ class MlaContext:
     def kernel_name(self) -> str:
         return self.lib.mla_kernel_name(self.h).decode()
 
+    def selftest_wait_timeout(self, limit_cycles: int = 1_000_000) -> int:
+        """Runs the bounded-wait self-test; returns the SM cycles the block waited before giving up."""
+        waited = C.c_uint32()
+        self._check(self.lib.mla_selftest_wait_timeout(self.h, limit_cycles, self._stream(), C.byref(waited)))
+        return waited.value
+
     def read_rows(self, layer: int, seq: int, row_begin: int, n: int) -> np.ndarray:
         out = np.empty((n, ROW), np.uint16)
         self._check(self.lib.mla_read_rows(self.h, layer, seq, row_begin, n, _np_ptr(out), self._stream()))

@@ -577,6 +577,30 @@ def test_cache_bookkeeping_and_errors(torch):
     ctx.close()
 
 
+def test_a_wait_that_runs_out_raises_the_status_bit_and_leaves_the_context_usable(torch, oracle):
+    """Failure detection on the device, without faulting it: the self-test block waits on a barrier nothing
+    completes, with a limit of a million cycles; the wait must give up (never hang, never trap), raise
+    ST_WAIT_TIMEOUT (4) in the status word, free its tensor memory and return.  The host reads the bit through
+    mla_status, which clears it, and the same context then computes a correct attention."""
+    case = synth.make_layer_case(4242, 128, [200], synth.DT_BF16)
+    ctx = make_ctx(case, capi.KERNEL_AUTO)
+    seqs = fill(torch, ctx, case)
+    assert ctx.status() == 0
+    waited = ctx.selftest_wait_timeout(1_000_000)
+    assert 1_000_000 <= waited < 400_000_000, waited          # gave up after the limit, within a fraction of a second
+    with pytest.raises(capi.MlaError) as ei:
+        ctx.status()
+    assert ei.value.code == 6 and "= 4" in str(ei.value)          # MLA_ERR_DEVICE, ST_WAIT_TIMEOUT
+    assert ctx.status() == 0                                   # reading cleared it
+    out = torch.zeros((1, 128, 128), dtype=torch.int16, device="cuda")
+    ctx.attend_rows(0, seqs, [200], _dev(torch, case.q), out)
+    check_close(_host(out)[0], oracle_out(oracle, case, 0), case.dt, "after the timed-out wait")
+    assert ctx.status() == 0
+    with pytest.raises(capi.MlaError):                         # limits beyond about a second are refused
+        ctx.selftest_wait_timeout(3_000_000_000)
+    ctx.close()
+
+
 def test_block_tables_are_permuted_pages(torch):
     from mugen_b200.mla import MlaContext
     ctx = MlaContext(n_layers=1, n_heads=2, dtype=synth.DT_F16, n_pages=64, max_seqs=2, max_seq_len=4096,

@@ -29,6 +29,26 @@ def test_host_units(exe):
     assert "host units ok" in out.stdout
 
 
+def test_host_units_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The CPU-only host logic (page table, free list, split-KV planner, rotary table) once more, compiled
+    with -fsanitize=address,undefined: an out-of-bounds table access, a use after free in the page
+    bookkeeping or a signed overflow in the planner's arithmetic would abort the run."""
+    capi.load()
+    src = os.path.join(ROOT, "tests", "host", "test_host.cpp")
+    libdir = os.path.dirname(capi.lib_path())
+    exe_san = str(tmp_path / "test_host_san")
+    subprocess.run(["g++", "-std=c++23", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+                    "-fno-omit-frame-pointer", "-ffp-contract=off", "-Wall", "-o", exe_san, src, f"-L{libdir}",
+                    "-l:libmugen_mla.so", f"-Wl,-rpath,{libdir}"], check=True)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
+    out = subprocess.run([exe_san, "units"], capture_output=True, text=True, env=env)
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert "host units ok" in out.stdout
+    out = subprocess.run([exe_san, "rope", "40.0", "4096", "10000.0", "0", "63", "64", "131071"], capture_output=True,
+                         text=True, env=env)
+    assert out.returncode == 0 and len(out.stdout.strip().splitlines()) == 4, out.stderr[-3000:]
+
+
 @pytest.mark.parametrize("factor,ctx,theta", [(40.0, 4096, 10000.0), (0.0, 0, 10000.0), (4.0, 32768, 1e6)])
 def test_rope_table_matches_checker_bit_for_bit(exe, oracle, factor, ctx, theta):
     """The library's host-built cos/sin rows (what the append kernel consumes) equal the values the

@@ -68,6 +68,67 @@ def _worker(rank, world, port, q, result):
         dist.destroy_process_group()
 
 
+def _absent_rank_worker(rank, world, port, result):
+    """Ranks 0..world-2 reach the all-gather of a step; the last rank joined the group but never makes the call
+    (it stands for a process that hung or died between steps, with nothing of its own in flight)."""
+    import datetime
+    import time
+
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    H = 4
+    mine = torch.full((1, H, sharding.PART), float(rank))
+    gathered = torch.zeros((world, 1, H, sharding.PART))
+    # one healthy exchange first: the group works
+    dist.all_gather_into_tensor(gathered.view(-1, H, sharding.PART), mine)
+    ok_first = bool((gathered[:, 0, 0, 0] == torch.arange(world, dtype=torch.float32)).all())
+    if rank == world - 1:
+        result.put((rank, ok_first, "absent", 0.0))
+        result.close()
+        result.join_thread()                               # the queue's feeder thread must flush before _exit
+        time.sleep(12)                                     # never arrives at the second exchange
+        os._exit(0)
+    t0 = time.time()
+    try:
+        dist.all_gather_into_tensor(gathered.view(-1, H, sharding.PART), mine)
+        outcome = "completed"
+    except Exception as e:                                 # the process group's timeout, reported on the host
+        outcome = "gave up: " + type(e).__name__
+    result.put((rank, ok_first, outcome, time.time() - t0))
+    result.close()
+    result.join_thread()
+    os._exit(0)                                            # the group is broken: no orderly teardown to wait for
+
+
+def test_a_rank_that_never_reaches_the_all_gather_is_detected_by_timeout():
+    """Failure detection without touching a GPU: the exchange step of the KV-range mode is a host-issued
+    collective, so a missing rank shows as a timeout error on the surviving ranks' host threads (seconds, set
+    on the process group), never as a device-side spin."""
+    import torch.multiprocessing as mp
+    world = 3
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, world, port, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(result.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok_first, outcome, waited in got:
+        assert ok_first, rank
+        if rank == world - 1:
+            assert outcome == "absent"
+        else:
+            assert outcome.startswith("gave up"), (rank, outcome)
+            assert 1.0 < waited < 30.0, (rank, waited)
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_kv_range_exchange_over_gloo(world):
     import torch.multiprocessing as mp
