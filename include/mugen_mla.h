@@ -177,6 +177,10 @@ int mla_step_end(mla_ctx* ctx);
 /* Rows in the current step and the number of KV segments they were split into. */
 int mla_step_info(const mla_ctx* ctx, uint32_t* rows, uint32_t* segments);
 
+/* How the planner spread the last planned step over the persistent attention workers (SM pairs or SMs): their
+ * number and the fewest / most cache pages any of them walks.  A balanced ragged batch has max - min <= one tile. */
+int mla_step_balance(const mla_ctx* ctx, uint32_t* workers, uint32_t* min_pages, uint32_t* max_pages);
+
 /* ---- KV-range sharding of one long sequence ----------------------------------------------- */
 /* Per-head partial softmax state of this shard for every row of the current step:
  * partial DEVICE float [rows][n_heads][514] = (m, l, acc[512]) with m the running maximum of

@@ -75,6 +75,9 @@ struct mla_ctx {
     char* meta_dev = nullptr;
     mla::StepMeta meta{};
 
+    // pages of the last planned step per persistent worker (mla_step_balance)
+    uint32_t plan_workers = 0, plan_min_pages = 0, plan_max_pages = 0;
+
     // step state
     bool in_step = false;
     std::vector<uint32_t> step_seqs, step_nnew;
@@ -223,6 +226,18 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
         cta_seg_begin.assign(1, 0);
     }
     const uint32_t G = uint32_t(segs.size()), W = uint32_t(cta_seg_begin.size()) - 1;
+    if (with_segments) {
+        c->plan_workers = W;
+        c->plan_min_pages = ~0u;
+        c->plan_max_pages = 0;
+        for (uint32_t w = 0; w < W; w++) {
+            uint32_t pages = 0;
+            for (uint32_t g = cta_seg_begin[w]; g < cta_seg_begin[w + 1]; g++) pages += segs[g].page_end - segs[g].page_begin;
+            c->plan_min_pages = std::min(c->plan_min_pages, pages);
+            c->plan_max_pages = std::max(c->plan_max_pages, pages);
+        }
+        if (W == 0) c->plan_min_pages = 0;
+    }
     size_t tbl_total = 0;
     std::vector<uint32_t> tbl_off(S);
     for (uint32_t i = 0; i < S; i++) {
@@ -990,6 +1005,15 @@ int mla_step_info(const mla_ctx* c, uint32_t* rows, uint32_t* segments)
     if (!c) return MLA_ERR_INVALID;
     if (rows) *rows = c->meta.rows;
     if (segments) *segments = c->meta.segs;
+    return MLA_OK;
+}
+
+int mla_step_balance(const mla_ctx* c, uint32_t* workers, uint32_t* min_pages, uint32_t* max_pages)
+{
+    if (!c) return MLA_ERR_INVALID;
+    if (workers) *workers = c->plan_workers;
+    if (min_pages) *min_pages = c->plan_min_pages;
+    if (max_pages) *max_pages = c->plan_max_pages;
     return MLA_OK;
 }
 

@@ -200,6 +200,12 @@ class MlaContext:
     def kernel_name(self) -> str:
         return self.lib.mla_kernel_name(self.h).decode()
 
+    def step_balance(self) -> tuple[int, int, int]:
+        """(workers, fewest pages, most pages) of the last planned step."""
+        w, lo, hi = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        self._check(self.lib.mla_step_balance(self.h, C.byref(w), C.byref(lo), C.byref(hi)))
+        return w.value, lo.value, hi.value
+
     def selftest_wait_timeout(self, limit_cycles: int = 1_000_000) -> int:
         """Runs the bounded-wait self-test; returns the SM cycles the block waited before giving up."""
         waited = C.c_uint32()

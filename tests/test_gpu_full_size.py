@@ -5,6 +5,8 @@ KV-range split against the unsplit sequence, a prefill chunk against single deco
 checker spot-checks on a few heads or sequences.  Inputs are generated on the device from a seed."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 
@@ -58,7 +60,7 @@ def test_ctx16384_decode_step_page_permutation_and_checker(torch, oracle):
     """configs[2] shape, 4 of its 64 sequences: one decode step at ctx 16384 through mla_step_layers.
     (a) two contexts holding the same logical caches under different page permutations give
     bit-identical outputs and appended rows; (b) appended rows equal the checker's bit for bit;
-    (c) two sequences agree with the CPU attention within the tolerance."""
+    (c) all four sequences, all 128 heads, agree with the CPU attention within the tolerance."""
     from mugen_b200.mla import MlaContext
     B, S = 4, 16383
     wk, wv, nw = _weights(1)
@@ -89,16 +91,16 @@ def test_ctx16384_decode_step_page_permutation_and_checker(torch, oracle):
     want_rows = oracle.append_rows(_bits(kv), [S] * B, nw, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, DT)
     assert np.array_equal(rows[0], want_rows)
     qh, ch = _bits(q), _bits(cache)
-    for b in (0, B - 1):
-        full = np.concatenate([ch[b], want_rows[b:b + 1]])
-        want = oracle.attention(qh[b], full, S + 1, wk, wv, synth.W_BF16, H, DT)
-        _close(outs[0][b], want, f"sequence {b} at ctx {S + 1}")
+    fulls = [np.concatenate([ch[b], want_rows[b:b + 1]]) for b in range(B)]
+    want = oracle.attention_batch(qh, fulls, [S + 1] * B, wk, wv, synth.W_BF16, H, DT, min(B, os.cpu_count() or 1))
+    for b in range(B):                                       # every sequence, all 128 heads
+        _close(outs[0][b], want[b], f"sequence {b} at ctx {S + 1}")
 
 
 def test_ctx131072_kv_range_split_equals_whole(torch, oracle):
     """configs[3] shape: one sequence of 131072 tokens (after the append), 128 heads.  The sequence held by
     one context, and cut into 4 page-aligned KV ranges held by 4 contexts whose partial states are merged,
-    give the same output within the tolerance; the first 8 heads are checked against the CPU attention."""
+    give the same output within the tolerance; the first 32 heads are checked against the CPU attention."""
     from mugen_b200.mla import MlaContext
     S, G = 131071, 4
     wk, wv, nw = _weights(2)
@@ -145,11 +147,11 @@ def test_ctx131072_kv_range_split_equals_whole(torch, oracle):
     assert shards[0].status() == 0
     _close(_bits(out_split)[0], _bits(out_whole)[0], "4 KV ranges against the whole sequence")
 
-    hs = 8                                                   # heads are independent: check the first 8 on the CPU
+    hs = 32                                                  # heads are independent: check the first 32 on the CPU
     full = np.concatenate([_bits(cache), want_row])
     want = oracle.attention(_bits(q)[0, :hs], full, S + 1, wk[:hs * 128], wv[:hs * 128], synth.W_BF16, hs, DT)
-    _close(_bits(out_whole)[0, :hs], want, "whole sequence, heads 0-7")
-    _close(_bits(out_split)[0, :hs], want, "merged ranges, heads 0-7")
+    _close(_bits(out_whole)[0, :hs], want, "whole sequence, heads 0-31")
+    _close(_bits(out_split)[0, :hs], want, "merged ranges, heads 0-31")
     for c in shards:
         c.close()
     whole.close()
@@ -209,4 +211,69 @@ def test_prefill_chunk_on_existing_context_with_ragged_decode_rows(torch, oracle
     full = np.concatenate([_bits(caches[b]), want_rows[b:b + 1]])
     want = oracle.attention(_bits(q)[b, :hs], full, dec_lens[b] + 1, wk[:hs * 128], wv[:hs * 128], synth.W_BF16, hs, DT)
     _close(got[b, :hs], want, f"decode row of length {dec_lens[b] + 1}, heads 0-7")
+    ctx.close()
+
+
+@pytest.mark.parametrize("start", [0, 8192])
+def test_config5_at_size_ragged_decode_rows_and_four_4096_token_chunks_in_one_step(torch, oracle, start):
+    """BASELINE.json configs[4] at its stated size, one layer, ONE scheduler step: 128 decode sequences with
+    log-uniform lengths 256..32768 plus 4 sequences that each append a 4096-token chunk at start_position 0 or 8192,
+    128 heads, bf16.  Chunk token t attends [0, start+t+1) (transformer.cpp:1325-1337).  Checked: every appended row
+    bit-equal to the checker; chunk tokens at the first, last and page-edge positions of two chunks, and the
+    longest and shortest decode rows, against the CPU attention on 8 heads; sequence counters moved by n_new."""
+    from mugen_b200.mla import MlaContext
+    N, n_chunks = 4096, 4
+    dec_lens = [int(n) for n in synth.ragged_lengths(42, 128, 256, 32768)]
+    wk, wv, nw = _weights(5 + start)
+    lens = dec_lens + [start] * n_chunks
+    n_new = [1] * len(dec_lens) + [N] * n_chunks
+    R = sum(n_new)
+    caches = [_rand_bf16(torch, (n, 576), 500 + i) if n else None for i, n in enumerate(lens)]
+    kv = _rand_bf16(torch, (R, 576), 61)
+    q = _rand_bf16(torch, (R, H, 192), 62, 0.9)
+    pages = sum((n + m + 63) // 64 + 1 for n, m in zip(lens, n_new)) + 8
+    ctx = MlaContext(n_layers=1, n_heads=H, dtype=DT, n_pages=pages, max_seqs=len(lens), max_seq_len=max(lens) + N + 64,
+                     max_rows=R, kernel=capi.KERNEL_AUTO, **YARN)
+    ctx.shuffle_free_pages(9)
+    ctx.set_layer_weights(0, wk, wv, synth.W_BF16, nw)
+    seqs = []
+    for c_, n in zip(caches, lens):
+        s = ctx.seq_create()
+        if n:
+            ctx.write_rows(0, s, 0, c_)
+        ctx.advance_seq_len(s, n)
+        seqs.append(s)
+    out = torch.zeros((R, H, 128), dtype=torch.int16, device="cuda")
+    ctx.step_begin(seqs, n_new)
+    ctx.step_layers(0, 1, kv[None], q[None], out[None])
+    ctx.step_end()
+    torch.cuda.synchronize()
+    assert ctx.status() == 0
+    assert [ctx.seq_len(s) for s in seqs] == [n + m for n, m in zip(lens, n_new)]
+    got, qh, kvh = _bits(out), _bits(q), _bits(kv)
+    # ---- appended rows: all 16,512 of them, bit for bit
+    pos = list(dec_lens)
+    for _ in range(n_chunks):
+        pos += [start + t for t in range(N)]
+    want_rows = oracle.append_rows(kvh, pos, nw, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, DT)
+    nd = len(dec_lens)
+    for b in range(nd):
+        assert np.array_equal(ctx.read_rows(0, seqs[b], dec_lens[b], 1)[0], want_rows[b]), f"decode row {b}"
+    for c in range(n_chunks):
+        r0 = nd + c * N
+        assert np.array_equal(ctx.read_rows(0, seqs[nd + c], start, N), want_rows[r0:r0 + N]), f"chunk {c}"
+    # ---- attention: sampled chunk tokens and decode rows against the CPU on 8 heads
+    hs = 8
+    for c in (0, n_chunks - 1):
+        r0 = nd + c * N
+        rows_c = want_rows[r0:r0 + N]
+        chunk_cache = rows_c if start == 0 else np.concatenate([_bits(caches[nd + c]), rows_c])
+        for t in (0, 1, 63, 64, 65, 2047, N - 65, N - 1):
+            want = oracle.attention(qh[r0 + t, :hs].copy(), chunk_cache, start + t + 1, wk[:hs * 128], wv[:hs * 128],
+                                    synth.W_BF16, hs, DT)
+            _close(got[r0 + t, :hs], want, f"chunk {c} token {t} (start {start}), heads 0-7")
+    for b in (int(np.argmax(dec_lens)), int(np.argmin(dec_lens)), 17):
+        full = np.concatenate([_bits(caches[b]), want_rows[b:b + 1]])
+        want = oracle.attention(qh[b, :hs].copy(), full, dec_lens[b] + 1, wk[:hs * 128], wv[:hs * 128], synth.W_BF16, hs, DT)
+        _close(got[b, :hs], want, f"decode row {b} of length {dec_lens[b] + 1}, heads 0-7")
     ctx.close()
