@@ -643,6 +643,48 @@ def sub_kv_range(torch, dist, world, rank, local, peak):
             "timing": "CUDA events over 4 steps after 2 warm-up steps, max over ranks"}
 
 
+def sub_prefill(torch, peak):
+    """BASELINE.json configs[4], chunk part: 4 sequences, each appending one 4096-token chunk in ONE step, causal
+    (token t attends [0, start+t+1)), at start_position 0 and 8192; 128 heads, bf16, one layer timed."""
+    from mugen_b200.mla import MlaContext
+    H, N, C, dt, tdt = 128, 4096, 4, synth.DT_BF16, torch.bfloat16
+    res = {"workload": "configs[4] chunks: 4 sequences x one 4096-token chunk in one step, causal, 128 heads, bf16, 1 layer"}
+    for start in (0, 8192):
+        R = N * C
+        ctx = MlaContext(n_layers=1, n_heads=H, dtype=dt, n_pages=C * ((start + N) // 64 + 2) + 8, max_seqs=C,
+                         max_seq_len=start + N + 64, max_rows=R, **ROPE_KW)
+        _weights(ctx, 1, H, dt, 7)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(77)
+        seqs = [ctx.seq_create() for _ in range(C)]
+        if start:
+            for sq in seqs:
+                rows = torch.randn((start, 576), device="cuda", dtype=torch.float32, generator=gen).to(tdt)
+                ctx.write_rows(0, sq, 0, rows.view(torch.int16))
+                ctx.advance_seq_len(sq, start)
+        q = (torch.randn((1, R, H, 192), device="cuda", dtype=torch.float32, generator=gen) * 0.9).to(tdt).view(torch.int16)
+        kv = torch.randn((1, R, 576), device="cuda", dtype=torch.float32, generator=gen).to(tdt).view(torch.int16)
+        out = torch.zeros((1, R, H, 128), device="cuda", dtype=torch.int16)
+
+        def step():
+            ctx.step_begin(seqs, [N] * C)
+            ctx.step_layers(0, 1, kv, q, out)
+            ctx.step_end()
+            for sq in seqs:                                          # roll the chunk back: the next step appends it again
+                ctx.truncate(sq, start)
+        ms = _time_steps(torch, step, 1, 3)
+        assert ctx.status() == 0
+        pairs = C * (N * start + N * (N + 1) // 2)                   # (query token, cached token) pairs
+        res[f"start_{start}"] = {"ms_per_layer_step": ms, "chunk_tokens_per_s_one_layer": R / (ms * 1e-3),
+                                 "chunk_tokens_per_s_61_layers_scaled": R / (ms * 1e-3) / 61,
+                                 "absorbed_form_tflops": pairs * H * 2.0 * (576 + 512) / (ms * 1e-3) / 1e12,
+                                 "path": ctx.kernel_name()}
+        ctx.close()
+        del q, kv, out
+        torch.cuda.empty_cache()
+    return res
+
+
 def run_extras(a, world, rank, local, only=""):
     import torch
     import torch.distributed as dist
@@ -663,6 +705,8 @@ def run_extras(a, world, rank, local, only=""):
             guarded("ragged", lambda: sub_ragged(torch, peak))
         if only in ("", "v2lite"):
             guarded("v2lite", lambda: sub_v2lite(torch, peak))
+        if only in ("", "prefill"):
+            guarded("prefill", lambda: sub_prefill(torch, peak))
     return res
 
 

@@ -125,8 +125,13 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
 {
     grid_launch_dependents();
     if (blockIdx.x >= absorb_blocks) {
-        grid_dependency_wait();
+        // The append touches nothing that an earlier kernel of the stream still reads or writes: its inputs are the
+        // caller's kv_a, constant tables and the step metadata (uploaded before the step's first kernel), and the
+        // slots it writes belong to this layer's pool, last read by this layer's attention in the PREVIOUS step.  So
+        // it works first and waits last; the wait only keeps "this kernel completes after its predecessors", which
+        // the kernels behind it rely on.
         append_rows<T>(app, (blockIdx.x - absorb_blocks) * APPEND_ROWS, status);
+        grid_dependency_wait();
         return;
     }
     extern __shared__ unsigned char absorb_tc5_smem[];

@@ -216,8 +216,11 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     std::vector<Segment> segs;
     std::vector<uint32_t> row_seg_begin, cta_seg_begin;
     if (with_segments) {
-        mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin,
-                                  c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? 2u : 1u);
+        if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
+            // a worker pays about four tiles' time per segment it starts (queries, pipeline fill, state drain)
+            mugen::mla::plan_min_makespan(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin, 2u, 4u);
+        else
+            mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin, 1u);
         if (segs.size() > c->max_segs)
             return fail(c, MLA_ERR_CAPACITY, "step needs " + std::to_string(segs.size()) +
                                                  " KV segments, workspace holds " + std::to_string(c->max_segs));

@@ -182,12 +182,31 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    // The step's metadata was uploaded by a copy that the stream ordered before the step's first kernel, so it may be
+    // read ahead of the wait: the chain of dependent loads that describes the first segment (segment -> row -> table
+    // offset -> page ids) then overlaps the previous kernel's tail instead of delaying the first TMA.
+    SegInfo seg0{};
+    const uint32_t* tbl0 = nullptr;
+    uint32_t page0[PAGES] = {0, 0};
+    if (seg_begin < seg_end) {
+        seg0 = load_seg(m, seg_begin);
+        tbl0 = m.tables + m.seq_tbl_off[m.row_seq[seg0.row]] + seg0.page_begin;
+        if (seg0.n_tiles) {
+#pragma unroll
+            for (int r = 0; r < PAGES; r++) page0[r] = tbl0[min(uint32_t(r), seg0.n_pages - 1)];
+        }
+    }
+    auto seg_info = [&](uint32_t seg) -> SegInfo { return seg == seg_begin ? seg0 : load_seg(m, seg); };
+    auto seg_table = [&](uint32_t seg, const SegInfo& si) -> const uint32_t* {
+        return seg == seg_begin ? tbl0 : m.tables + m.seq_tbl_off[m.row_seq[si.row]] + si.page_begin;
+    };
     grid_dependency_wait();          // queries, new cache rows and the state records belong to earlier kernels until here
 
     // Page of super-tile j that block `r` stages as K (and whose tokens are columns 64r .. 64r+63 of
     // the score tile).  A segment with an odd page count repeats its last page in the second half:
     // finite data whose scores the softmax masks.
     auto page_of = [&](const uint32_t* tbl, const SegInfo& s, uint32_t j, uint32_t r) -> uint32_t {
+        if (tbl == tbl0 && j == 0) return page0[r];
         const uint32_t i = min(PAGES * j + r, s.n_pages - 1);
         return tbl[i];
     };
@@ -200,9 +219,9 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             uint32_t t = 0, nseg = 0;
             bool ok = true;
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
-                const SegInfo s = load_seg(m, seg);
+                const SegInfo s = seg_info(seg);
                 if (s.n_tiles == 0) continue;
-                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
+                const uint32_t* tbl = seg_table(seg, s);
                 ok = mbar_wait<kSleep>(bar(B_QEMPTY), (nseg & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(bar(B_QFULL), 2 * Q_BYTES);
@@ -238,9 +257,9 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             uint32_t t = 0;
             bool ok = true;
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
-                const SegInfo s = load_seg(m, seg);
+                const SegInfo s = seg_info(seg);
                 if (s.n_tiles == 0) continue;
-                const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]] + s.page_begin;
+                const uint32_t* tbl = seg_table(seg, s);
                 if (PREFETCH_TILES > 0)
                     for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) {
                         const uint32_t pgid = page_of(tbl, s, jj, rank);
@@ -282,7 +301,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
             uint32_t t = 0, nseg = 0;
             bool ok = true;
             for (uint32_t seg = seg_begin; seg < seg_end && ok; seg++) {
-                const SegInfo s = load_seg(m, seg);
+                const SegInfo s = seg_info(seg);
                 if (s.n_tiles == 0) continue;
                 if (is_qk) ok = mbar_wait<kSleepCluster>(bar(B_QFULL), nseg & 1, abort_flag, status);
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
@@ -358,7 +377,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         const uint32_t r_flag = map_to_rank(base + OFF_MISC + M_FLAG, peer);
         const uint32_t r_alpha = map_to_rank(base + OFF_MISC + M_ALPHA, peer);
         float m_used = -INFINITY, l_part = 0.0f;
-        uint32_t t = 0, nseg = 0, nb[2] = {0, 0};             // nb: uses of SYNCB[par] so far
+        uint32_t t = 0, nseg = 0, na[2] = {0, 0}, nb[2] = {0, 0};   // na / nb: uses of SYNCA[par] / SYNCB[par] so far
         bool fail = false;
         auto wait_w = [&](uint32_t b, uint32_t parity) {              // completion of tensor-core / TMA work
             if (!fail) fail = !mbar_wait<kSleep>(b, parity, abort_flag, status);
@@ -380,7 +399,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         };
         bool stop = false;
         for (uint32_t seg = seg_begin; seg < seg_end && !stop; seg++) {
-            const SegInfo s = load_seg(m, seg);
+            const SegInfo s = seg_info(seg);
             if (s.n_tiles == 0) {
                 // nothing to attend: each block writes its 256 dims of every head, and (m, l) of its own heads
                 for (uint32_t h = 0; h < 2 * HG; h++) {
@@ -438,10 +457,20 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
 #pragma unroll
                 for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
                 mx *= scale_log2;
+                // The first tile of a segment sets every head's reference maximum, but there is no O^T to rescale yet
+                // (its PV starts a fresh accumulation), so the twin block has nothing to learn from it: the four
+                // token quarters of a head meet inside the block and the two cluster rounds are skipped.  Both blocks
+                // of a pair walk the same segments, so they skip the same rounds.
+                const bool first = j == 0;
+                if (first) {
+                    half_max[tq * HG + hl] = mx;
+                    if (group_or(fail)) { stop = true; break; }
+                    m_used = fmaxf(fmaxf(half_max[hl], half_max[HG + hl]), fmaxf(half_max[2 * HG + hl], half_max[3 * HG + hl]));
+                }
                 // does any head of the pair have to move its reference maximum on this tile?
-                const bool need = (j == 0) || (mx > m_used + RESCALE_THRESHOLD);
+                const bool need = !first && (mx > m_used + RESCALE_THRESHOLD);
                 const bool warp_need = __any_sync(0xffffffffu, need);
-                if (lane == 0 && !fail) {
+                if (lane == 0 && !fail && !first) {
                     if (warp_need) {
                         atomicOr(const_cast<uint32_t*>(&need_flag[par]), 1u);
                         asm volatile("red.relaxed.cluster.shared::cluster.or.b32 [%0], %1;\n" ::"r"(r_flag + 4 * par), "r"(1u) : "memory");
@@ -463,9 +492,13 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     sum += p0 + p1;
                     pk[i / 2] = Elem<T>::pack2(p0, p1);
                 }
-                wait_x(bar(B_SYNCA0 + par), (t >> 1) & 1);
-                if (group_or(fail)) { stop = true; break; }
-                const bool slow = need_flag[par] != 0;
+                bool slow = false;
+                if (!first) {
+                    wait_x(bar(B_SYNCA0 + par), na[par] & 1);
+                    na[par]++;
+                    if (group_or(fail)) { stop = true; break; }
+                    slow = need_flag[par] != 0;
+                }
                 if (slow) {
                     // exchange the token quarters' maxima inside the block, decide per head, publish the
                     // scale factors to both blocks, and redo the exponentials
@@ -473,8 +506,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                     half_max[tq * HG + hl] = mx;
                     group_or(false);
                     const float mrow = fmaxf(fmaxf(half_max[hl], half_max[HG + hl]), fmaxf(half_max[2 * HG + hl], half_max[3 * HG + hl]));
-                    if (j == 0) { m_used = mrow; alpha = 0.0f; }
-                    else if (mrow > m_used + RESCALE_THRESHOLD) { alpha = fast_ex2(m_used - mrow); m_used = mrow; }
+                    if (mrow > m_used + RESCALE_THRESHOLD) { alpha = fast_ex2(m_used - mrow); m_used = mrow; }
                     if (tq == 0) {
                         alpha_all[par * 128 + rank * HG + hl] = alpha;
                         asm volatile("st.relaxed.cluster.shared::cluster.f32 [%0], %1;\n"
@@ -502,7 +534,7 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 wait_w(bar(B_PEMPTY), (t - 1) & 1);
                 if (fail) continue;            // carried to the next barrier
                 tc_fence_after();
-                if (slow && j > 0) {
+                if (slow) {
                     // O^T[this block's dims][128 heads] *= alpha[head]; each warp group takes one chunk
 #pragma unroll 1
                     for (int c = 0; c < 4; c++) {

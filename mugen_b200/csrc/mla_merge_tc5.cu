@@ -43,7 +43,7 @@ constexpr int NUM_THREADS = 512;
 constexpr uint32_t TMEM_COLS = 128;
 
 
-template <typename T>
+template <typename T, bool kSmall>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float* __restrict__ recs,
                          const uint32_t* __restrict__ row_seg_begin, uint32_t n_parts, T* __restrict__ out,
@@ -110,10 +110,68 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
             else               { pb4[x] = 0; pe4[x] = n_parts; }
         }
     }
+    // Small batches (at most 16 rows in this block, e.g. 8 sequences per GPU): a warp has one row and sweeps its parts
+    // ONCE for all 512 dims (a lane owns dims 64*k + 2*lane (+1), k = 0..7), so a row of ~10 parts costs three round
+    // trips to memory instead of six; the two halves of the projection then only differ in which eight of the lane's
+    // sixteen sums they write as operands.
+    constexpr bool small = kSmall;                        // chosen at launch: the whole step has at most 16 rows
+    float acc_s[kSmall ? 16 : 1], inv_s = 0.0f;
+    if constexpr (kSmall) {
+        float M = -INFINITY, L = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 16; k++) acc_s[k] = 0.0f;
+        const uint32_t rw = r0 + warp;
+        for (uint32_t p = pb4[0]; p < pe4[0]; p += 4) {
+            float2 ml[4], v[4][8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const bool on = p + i < pe4[0];
+                const float* rc = rec_of(rw, on ? p + i : pb4[0]);
+                ml[i] = on ? *reinterpret_cast<const float2*>(rc) : make_float2(-INFINITY, 0.0f);
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    v[i][k] = on ? *reinterpret_cast<const float2*>(rc + 2 + 64 * k + 2 * lane) : make_float2(0.0f, 0.0f);
+            }
+            const float Mn = fmaxf(fmaxf(M, ml[0].x), fmaxf(fmaxf(ml[1].x, ml[2].x), ml[3].x));
+            if (Mn > -INFINITY) {
+                const float sc = exp2f(M - Mn);
+                L *= sc;
+#pragma unroll
+                for (int k = 0; k < 16; k++) acc_s[k] *= sc;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float w = exp2f(ml[i].x - Mn);
+                    L = fmaf(w, ml[i].y, L);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        acc_s[2 * k] = fmaf(w, v[i][k].x, acc_s[2 * k]);
+                        acc_s[2 * k + 1] = fmaf(w, v[i][k].y, acc_s[2 * k + 1]);
+                    }
+                }
+                M = Mn;
+            }
+        }
+        inv_s = L > 0.0f ? 1.0f / L : 0.0f;
+    }
 #pragma unroll 1
     for (int kh = 0; kh < 2; kh++) {
+        if constexpr (kSmall) {
+            // the first half's MMAs read the operand buffers until they complete
+            if (kh == 1) ok = mbar_wait(bar_mma, 0, fail_flag, status);
+            const uint32_t rr = warp;
+            const uint32_t off = rr * 128 + (((lane / 4) ^ (rr & 7)) << 4) + (lane % 4) * 4;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float o0 = (kh == 0 ? acc_s[2 * k] : acc_s[8 + 2 * k]) * inv_s;
+                const float o1 = (kh == 0 ? acc_s[2 * k + 1] : acc_s[8 + 2 * k + 1]) * inv_s;
+                const T h0 = Elem<T>::from_f32(o0), h1 = Elem<T>::from_f32(o1);
+                *reinterpret_cast<uint32_t*>(sm + OFF_AHI + k * A_SUB + off) = Elem<T>::pack2(o0, o1);
+                *reinterpret_cast<uint32_t*>(sm + OFF_ALO + k * A_SUB + off) =
+                    Elem<T>::pack2(o0 - Elem<T>::to_f32(h0), o1 - Elem<T>::to_f32(h1));
+            }
+        }
 #pragma unroll 1
-        for (int pr = 0; pr < 2; pr++) {
+        for (int pr = 0; pr < 2 && !small; pr++) {
             uint32_t p[2], pe[2], rw[2];
             float M[2], L[2], acc[2][8];
 #pragma unroll
@@ -243,19 +301,22 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
 
 }  // namespace
 
-int merge_tc5_configure()
+template <typename K>
+static cudaError_t configure_one(K kernel)
 {
-    cudaError_t e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_BYTES);
-    if (e != cudaSuccess) return int(e);
-    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM_BYTES);
-    if (e != cudaSuccess) return int(e);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
     // every kernel of a layer-step asks for the same (maximal) shared-memory carve-out, so the SMs are not
     // re-partitioned between consecutive launches
-    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e != cudaSuccess) return int(e);
-    e = cudaFuncSetAttribute(merge_outproj_tc5_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
+int merge_tc5_configure()
+{
+    cudaError_t e = configure_one(merge_outproj_tc5_kernel<__half, false>);
+    if (e == cudaSuccess) e = configure_one(merge_outproj_tc5_kernel<__half, true>);
+    if (e == cudaSuccess) e = configure_one(merge_outproj_tc5_kernel<__nv_bfloat16, false>);
+    if (e == cudaSuccess) e = configure_one(merge_outproj_tc5_kernel<__nv_bfloat16, true>);
     return int(e);
 }
 
@@ -266,11 +327,15 @@ int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
     dim3 grid(H, (rows + MT - 1) / MT);
+    auto go = [&](auto kernel, auto* o) {
+        return int(launch_pdl(kernel, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin, n_parts, o, rows, H, status));
+    };
+    const bool small = rows <= 16;
     if (dtype == 0)
-        return int(launch_pdl(merge_outproj_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin,
-                              n_parts, static_cast<__half*>(out), rows, H, status));
-    return int(launch_pdl(merge_outproj_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs,
-                          row_seg_begin, n_parts, static_cast<__nv_bfloat16*>(out), rows, H, status));
+        return small ? go(merge_outproj_tc5_kernel<__half, true>, static_cast<__half*>(out))
+                     : go(merge_outproj_tc5_kernel<__half, false>, static_cast<__half*>(out));
+    return small ? go(merge_outproj_tc5_kernel<__nv_bfloat16, true>, static_cast<__nv_bfloat16*>(out))
+                 : go(merge_outproj_tc5_kernel<__nv_bfloat16, false>, static_cast<__nv_bfloat16*>(out));
 }
 
 }  // namespace mla

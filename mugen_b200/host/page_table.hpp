@@ -231,4 +231,68 @@ inline void plan_balanced(const std::vector<uint32_t>& attend_lens, uint32_t pag
     worker_seg_begin[workers] = uint32_t(segs.size());
 }
 
+// The same plan with a price on every segment.  A worker pays a fixed cost each time it starts a segment (load the
+// row's queries, fill the pipeline, drain the partial state: about four tiles' worth of time on the SM-pair kernel),
+// so equal shares of PAGES are not equal shares of TIME: with 8 rows over 74 workers the equal-share plan hands the
+// workers that straddle a row boundary two segments for the price of a worker with one.  Here the makespan
+// T = max over workers of sum(seg_overhead + units of the segment) is minimised by bisection: for a trial T the rows
+// are poured into the workers in order, a worker closing when another unit (plus the overhead, if it would have to
+// start a segment for it) no longer fits.  Units are `granule_pages` pages (the kernel's tile); cuts inside a row
+// fall on unit boundaries.  seg_overhead = 0 reproduces equal shares up to rounding.
+inline void plan_min_makespan(const std::vector<uint32_t>& attend_lens, uint32_t page_tokens, uint32_t workers,
+                              std::vector<Segment>& segs, std::vector<uint32_t>& row_seg_begin,
+                              std::vector<uint32_t>& worker_seg_begin, uint32_t granule_pages, uint32_t seg_overhead)
+{
+    const uint32_t rows = uint32_t(attend_lens.size());
+    std::vector<uint32_t> pages(rows), units(rows);
+    uint64_t total = 0;
+    for (uint32_t r = 0; r < rows; r++) {
+        pages[r] = (attend_lens[r] + page_tokens - 1) / page_tokens;
+        units[r] = (pages[r] + granule_pages - 1) / granule_pages;
+        total += units[r];
+    }
+    workers = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(workers, total)));
+    std::vector<uint32_t> seg_worker;
+    // pours the rows into workers of capacity T; returns the number of workers used (emit: also records the plan)
+    auto pour = [&](uint64_t T, bool emit) -> uint64_t {
+        uint64_t used = 1, cur = 0;
+        if (emit) { segs.clear(); seg_worker.clear(); row_seg_begin.assign(rows + 1, 0); }
+        for (uint32_t r = 0; r < rows; r++) {
+            if (emit) row_seg_begin[r] = uint32_t(segs.size());
+            if (units[r] == 0) {
+                if (emit) { segs.push_back({r, 0, 0}); seg_worker.push_back(uint32_t(used - 1)); }
+                continue;
+            }
+            uint32_t done = 0;
+            while (done < units[r]) {
+                if (cur + seg_overhead + 1 > T && cur > 0) { used++; cur = 0; }      // no room to start a segment here
+                const uint64_t room = T > cur + seg_overhead ? T - cur - seg_overhead : 1;
+                const uint32_t take = uint32_t(std::min<uint64_t>(units[r] - done, room));
+                if (emit) {
+                    segs.push_back({r, std::min(pages[r], done * granule_pages), std::min(pages[r], (done + take) * granule_pages)});
+                    seg_worker.push_back(uint32_t(used - 1));
+                }
+                done += take;
+                cur += seg_overhead + take;
+            }
+        }
+        return used;
+    };
+    uint64_t lo = 1, hi = total + uint64_t(seg_overhead) * (rows + workers) + 1;
+    while (lo < hi) {
+        const uint64_t mid = (lo + hi) / 2;
+        if (pour(mid, false) <= workers) hi = mid; else lo = mid + 1;
+    }
+    const uint64_t used = total ? pour(lo, true) : pour(1, true);
+    row_seg_begin[rows] = uint32_t(segs.size());
+    const uint32_t W = total ? uint32_t(std::max<uint64_t>(used, 1)) : workers;
+    worker_seg_begin.assign(W + 1, uint32_t(segs.size()));
+    uint32_t s = 0;
+    for (uint32_t c = 0; c < W; c++) {
+        worker_seg_begin[c] = s;
+        while (s < segs.size() && seg_worker[s] == c) s++;
+    }
+    worker_seg_begin[W] = uint32_t(segs.size());
+}
+
 }  // namespace mugen::mla

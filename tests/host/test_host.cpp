@@ -126,6 +126,51 @@ static void test_planner()
     lens.clear();
     plan_balanced(lens, 64, 148, segs, rsb, wsb);
     CHECK(segs.empty() && rsb.size() == 1 && wsb.back() == 0);
+
+    // ---- the plan that prices segments: coverage, order, cuts on tile boundaries, and a makespan no worse than
+    // the equal-share plan's under the same price
+    auto cost_of = [&](const std::vector<Segment>& sg, const std::vector<uint32_t>& ws, uint32_t ovh) {
+        uint64_t worst = 0;
+        for (size_t w = 0; w + 1 < ws.size(); w++) {
+            uint64_t c = 0;
+            for (uint32_t g = ws[w]; g < ws[w + 1]; g++) {
+                const uint32_t n = sg[g].page_end - sg[g].page_begin;
+                if (n) c += ovh + (n + 1) / 2;
+            }
+            worst = std::max(worst, c);
+        }
+        return worst;
+    };
+    for (auto cfg : std::vector<std::pair<std::vector<uint32_t>, uint32_t>>{
+             {std::vector<uint32_t>(8, 16384), 74}, {std::vector<uint32_t>(64, 16384), 74}, {std::vector<uint32_t>(1, 131072), 74},
+             {{0, 1, 64, 65, 0, 1000, 0, 32768, 300}, 74}, {std::vector<uint32_t>(3, 100), 148}, {{}, 74}}) {
+        const auto& ls = cfg.first;
+        std::vector<Segment> s2, s1;
+        std::vector<uint32_t> r2, w2, r1, w1;
+        plan_min_makespan(ls, 64, cfg.second, s2, r2, w2, 2, 4);
+        CHECK(r2.size() == ls.size() + 1 && w2.back() == s2.size() && w2.size() <= cfg.second + 1u);
+        for (uint32_t r = 0; r < ls.size(); r++) {
+            uint32_t next = 0;
+            CHECK(r2[r + 1] > r2[r]);                                   // every row keeps at least one segment
+            for (uint32_t g = r2[r]; g < r2[r + 1]; g++) {
+                CHECK(s2[g].row == r && s2[g].page_begin == next && s2[g].page_begin % 2 == 0);
+                CHECK(s2[g].page_end > next || ls[r] == 0);
+                next = s2[g].page_end;
+            }
+            CHECK(next == (ls[r] + 63) / 64);
+        }
+        for (size_t w = 0; w + 1 < w2.size(); w++) CHECK(w2[w] <= w2[w + 1]);
+        if (!ls.empty()) {
+            plan_balanced(ls, 64, cfg.second, s1, r1, w1, 2);
+            CHECK(cost_of(s2, w2, 4) <= cost_of(s1, w1, 4));
+        }
+    }
+    {   // 8 rows of 128 tiles over 74 workers: nobody gets two segments for the price of one
+        std::vector<Segment> s2;
+        std::vector<uint32_t> r2, w2;
+        plan_min_makespan(std::vector<uint32_t>(8, 16384), 64, 74, s2, r2, w2, 2, 4);
+        CHECK(cost_of(s2, w2, 4) <= 19);
+    }
 }
 
 static void test_wrapper_without_gpu()
