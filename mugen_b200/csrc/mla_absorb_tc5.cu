@@ -79,8 +79,23 @@ __device__ __forceinline__ void append_rows(const AppendArgs& a, uint32_t first_
         }
     }
     constexpr int kChunks = kRow * 2 / 16;   // 72 x 16 bytes
-    if (live && tid < kChunks)
-        reinterpret_cast<uint4*>(xin[g])[tid] = reinterpret_cast<const uint4*>(kv_a + size_t(r) * kRow)[tid];
+    // Every global load of the row is issued here, before the first barrier: the row itself, the rotation's cos/sin
+    // and this thread's four norm weights.  Left where they are used they would form a chain of three dependent
+    // round trips to memory (~1 us each) in a kernel whose whole budget is a few microseconds.
+    uint4 row_chunk = make_uint4(0, 0, 0, 0);
+    float cs = 0.0f, sn = 0.0f, nw[kRank / 128];
+#pragma unroll
+    for (int k = 0; k < kRank / 128; k++) nw[k] = 0.0f;
+    if (live) {
+        if (tid < kChunks) row_chunk = reinterpret_cast<const uint4*>(kv_a + size_t(r) * kRow)[tid];
+        if (tid >= 32 && tid < 64) {
+            cs = a.cos_sin[size_t(pos) * kRope + (tid - 32)];
+            sn = a.cos_sin[size_t(pos) * kRope + 32 + (tid - 32)];
+        }
+#pragma unroll
+        for (int k = 0; k < kRank / 128; k++) nw[k] = Elem<T>::to_f32(norm_w[tid + 128 * k]);
+    }
+    if (live && tid < kChunks) reinterpret_cast<uint4*>(xin[g])[tid] = row_chunk;
     __syncthreads();
     if (live) {
         for (int i = tid; i < kRank; i += 128) {
@@ -89,12 +104,10 @@ __device__ __forceinline__ void append_rows(const AppendArgs& a, uint32_t first_
         }
         if (tid >= 32 && tid < 64) {
             const int i = tid - 32;
-            const float c = a.cos_sin[size_t(pos) * kRope + i];
-            const float s = a.cos_sin[size_t(pos) * kRope + 32 + i];
             const float x0 = Elem<T>::to_f32(xin[g][kRank + i]);
             const float x1 = Elem<T>::to_f32(xin[g][kRank + 32 + i]);
-            xout[g][kRank + i]      = Elem<T>::from_f32(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
-            xout[g][kRank + 32 + i] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s)));
+            xout[g][kRank + i]      = Elem<T>::from_f32(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+            xout[g][kRank + 32 + i] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(x0, sn)));
         }
     }
     __syncthreads();
@@ -107,9 +120,11 @@ __device__ __forceinline__ void append_rows(const AppendArgs& a, uint32_t first_
     __syncthreads();
     if (live) {
         const float rinv = rinv_s[g];
-        for (int i = tid; i < kRank; i += 128) {
+#pragma unroll
+        for (int k = 0; k < kRank / 128; k++) {
+            const int i = tid + 128 * k;
             const float v = __fmul_rn(Elem<T>::to_f32(xin[g][i]), rinv);
-            xout[g][i] = Elem<T>::from_f32(__fmul_rn(v, Elem<T>::to_f32(norm_w[i])));
+            xout[g][i] = Elem<T>::from_f32(__fmul_rn(v, nw[k]));
         }
     }
     __syncthreads();

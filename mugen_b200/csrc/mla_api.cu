@@ -217,8 +217,8 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     std::vector<uint32_t> row_seg_begin, cta_seg_begin;
     if (with_segments) {
         if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
-            // a worker pays about four tiles' time per segment it starts (queries, pipeline fill, state drain)
-            mugen::mla::plan_min_makespan(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin, 2u, 4u);
+            // a worker pays about five tiles' time per segment it starts (queries, pipeline fill, state drain: ~10 us)
+            mugen::mla::plan_min_makespan(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin, 2u, 5u);
         else
             mugen::mla::plan_balanced(lens, mla::kPage, c->workers, segs, row_seg_begin, cta_seg_begin, 1u);
         if (segs.size() > c->max_segs)
@@ -361,8 +361,9 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     const bool timed = c->profiling && c->prof_used < c->prof_events.size() && (c->prof_seq++ % c->prof_stride) == 0;
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
+        // short work lists (few sequences on this GPU) are bound by load latency, not bandwidth: prefetch one tile ahead
         e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer_pool(c, layer), layer, c->cfg.n_pages, m, c->recs, H,
-                                           c->status_dev, st);
+                                           c->plan_max_pages <= 64 ? 1u : 0u, c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)
         e = mla::launch_decode_tc5(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else

@@ -85,14 +85,13 @@ constexpr int SOFTMAX_THREADS = 256;
 constexpr int PAIR_SOFTMAX_WARPS = 16;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
-// L2 prefetch distance in tiles (0 = off): every block pulls "its" whole page towards L2 that many tiles ahead as
-// ONE linear request of 73,728 contiguous bytes, so DRAM sees a sequential burst per page instead of thirteen
-// boxes of 128- or 256-byte pieces 1,152 bytes apart, spread over a tile period (a tensor-map prefetch of the
-// page walks it in the same strided order and changed nothing).
-#ifndef MLA_PAIR128_PREFETCH
-#define MLA_PAIR128_PREFETCH 0
-#endif
-constexpr int PREFETCH_TILES = MLA_PAIR128_PREFETCH;
+// L2 prefetch (kernel argument prefetch_tiles, 0 = off): every block pulls "its" whole page towards L2 that many
+// tiles ahead as ONE linear request of 73,728 contiguous bytes.  Each K sub-tile buffer is re-loaded as soon as the
+// MMAs that read it complete and is needed again one tile later, so the re-load's latency sits on the tile loop:
+// with few sequences per GPU (HBM far from saturated) turning an HBM miss into an L2 hit shortens the tile period
+// (8 sequences: 47.7 -> 45.3 us per launch at distance 1; distances 2 and 4 queue more requests in front of the
+// demand loads and lose again), while at batch 64, where HBM bandwidth is the co-limit, it changes nothing
+// (267 -> 268 us), so the host turns it on only for short work lists.
 constexpr int K_ROUNDS = (NSUB + N_QK - 1) / N_QK;   // 3: the issuers free sub-tiles {0-3}, {4-7}, {8} together
 enum { B_QFULL = 0, B_QEMPTY, B_KFULL, B_KEMPTY = B_KFULL + NSUB, B_VFULL = B_KEMPTY + K_ROUNDS, B_VEMPTY = B_VFULL + 4,
        B_SFULL = B_VEMPTY + PAGES, B_SEMPTY, B_PFULL, B_PEMPTY, B_OFULL, B_SYNCA0, B_SYNCA1, B_SYNCB0, B_SYNCB1, B_COUNT };
@@ -120,7 +119,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __grid_constant__ CUtensorMap map_kv64,
                           const __grid_constant__ CUtensorMap map_q, const unsigned char* __restrict__ pool_layer,
                           uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
-                          float scale_log2, uint32_t* __restrict__ status)
+                          float scale_log2, uint32_t prefetch_tiles, uint32_t* __restrict__ status)
 {
     extern __shared__ __align__(1024) unsigned char sm[];
     const uint32_t base = smem_u32(sm);
@@ -200,6 +199,14 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     auto seg_table = [&](uint32_t seg, const SegInfo& si) -> const uint32_t* {
         return seg == seg_begin ? tbl0 : m.tables + m.seq_tbl_off[m.row_seq[si.row]] + si.page_begin;
     };
+    // L2 is the point of coherence, so pulling cache lines towards it ahead of the wait is safe even for the page
+    // that the append of this layer-step is still writing: the first tiles' loads then find their pages in L2.
+    if (warp == N_QK + N_PV + 1 && lane == 0 && seg_begin < seg_end) {
+        for (uint32_t jj = 0; jj < min(2u, seg0.n_tiles); jj++) {
+            const uint32_t pgid = tbl0[min(PAGES * jj + rank, seg0.n_pages - 1)];
+            if (pgid < n_pages) bulk_prefetch_l2(pool_layer + size_t(pgid) * (kPage * kRow * 2), kPage * kRow * 2);
+        }
+    }
     grid_dependency_wait();          // queries, new cache rows and the state records belong to earlier kernels until here
 
     // Page of super-tile j that block `r` stages as K (and whose tokens are columns 64r .. 64r+63 of
@@ -260,14 +267,14 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                 const SegInfo s = seg_info(seg);
                 if (s.n_tiles == 0) continue;
                 const uint32_t* tbl = seg_table(seg, s);
-                if (PREFETCH_TILES > 0)
-                    for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) {
-                        const uint32_t pgid = page_of(tbl, s, jj, rank);
-                        if (pgid < n_pages) bulk_prefetch_l2(pool_layer + size_t(pgid) * (kPage * kRow * 2), kPage * kRow * 2);
-                    }
+                // tile 0 is demand-loaded right now; tiles 1 .. prefetch_tiles-1 have no earlier tile to ride on
+                for (uint32_t jj = 1; jj < min(prefetch_tiles, s.n_tiles); jj++) {
+                    const uint32_t pgid = page_of(tbl, s, jj, rank);
+                    if (pgid < n_pages) bulk_prefetch_l2(pool_layer + size_t(pgid) * (kPage * kRow * 2), kPage * kRow * 2);
+                }
                 for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
-                    if (PREFETCH_TILES > 0 && j + PREFETCH_TILES < s.n_tiles) {
-                        const uint32_t pgid = page_of(tbl, s, j + PREFETCH_TILES, rank);
+                    if (prefetch_tiles > 0 && j + prefetch_tiles < s.n_tiles) {
+                        const uint32_t pgid = page_of(tbl, s, j + prefetch_tiles, rank);
                         if (pgid < n_pages) bulk_prefetch_l2(pool_layer + size_t(pgid) * (kPage * kRow * 2), kPage * kRow * 2);
                     }
 #pragma unroll 1
@@ -630,7 +637,8 @@ int decode_tc5_pair128_configure()
 // tmaps: the context's tensor-map array (kMapPoolSub = one K sub-tile, kMapPoolV = V boxes, kMapQueries = Q').
 // layer_pool: the layer's slice of the cache pool (linear L2 prefetch).
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
-                              const StepMeta& m, float* recs, uint32_t H, uint32_t* status, cudaStream_t st)
+                              const StepMeta& m, float* recs, uint32_t H, uint32_t prefetch_tiles, uint32_t* status,
+                              cudaStream_t st)
 {
     if (m.ctas == 0) return 0;
     const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);
@@ -638,9 +646,9 @@ int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_po
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
         return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV], maps[kMapQueries],
-                              static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, status));
+                              static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles, status));
     return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV],
-                          maps[kMapQueries], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, status));
+                          maps[kMapQueries], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles, status));
 }
 
 }  // namespace mla
