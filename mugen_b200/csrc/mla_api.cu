@@ -360,10 +360,14 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     int e;
     const bool timed = c->profiling && c->prof_used < c->prof_events.size() && (c->prof_seq++ % c->prof_stride) == 0;
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used].first, st));
+    // the W_UK the stream will want next: the following layer's (the first layer's after the last: the next step)
+    const LayerW& nlw = c->layers[(layer + 1) % c->cfg.n_layers];
+    const void* next_w = nlw.set ? nlw.w_uk : nullptr;
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128)
         // short work lists (few sequences on this GPU) are bound by load latency, not bandwidth: prefetch one tile ahead
         e = mla::launch_decode_tc5_pair128(int(c->cfg.dtype), c->tmaps, layer_pool(c, layer), layer, c->cfg.n_pages, m, c->recs, H,
-                                           c->plan_max_pages <= 64 ? 1u : 0u, c->status_dev, st);
+                                           c->plan_max_pages <= 64 ? 1u : 0u, next_w, next_w ? uint32_t(size_t(H) * mla::kNope * mla::kRank * 2) : 0u,
+                                           c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)
         e = mla::launch_decode_tc5(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else

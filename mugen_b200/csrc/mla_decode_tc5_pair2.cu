@@ -119,7 +119,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __grid_constant__ CUtensorMap map_kv64,
                           const __grid_constant__ CUtensorMap map_q, const unsigned char* __restrict__ pool_layer,
                           uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
-                          float scale_log2, uint32_t prefetch_tiles, uint32_t* __restrict__ status)
+                          float scale_log2, uint32_t prefetch_tiles, const unsigned char* __restrict__ next_weights,
+                          uint32_t next_weights_bytes, uint32_t* __restrict__ status)
 {
     extern __shared__ __align__(1024) unsigned char sm[];
     const uint32_t base = smem_u32(sm);
@@ -149,27 +150,29 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
         return;
     }
 
-    if (tid == 0) {
-        *abort_flag = 0;
-        need_flag[0] = need_flag[1] = 0;
-        mbar_init(bar(B_QFULL), 1);
-        mbar_init(bar(B_QEMPTY), N_QK);
-        for (int c = 0; c < NSUB; c++) mbar_init(bar(B_KFULL + c), 1);
-        for (int rd = 0; rd < K_ROUNDS; rd++) mbar_init(bar(B_KEMPTY + rd), min(N_QK, NSUB - N_QK * rd));
-        for (int v = 0; v < 4; v++) mbar_init(bar(B_VFULL + v), 1);
-        for (int pg = 0; pg < PAGES; pg++) mbar_init(bar(B_VEMPTY + pg), N_PV);
-        mbar_init(bar(B_SFULL), N_QK);
-        mbar_init(bar(B_SEMPTY), PAIR_SOFTMAX_WARPS);
-        mbar_init(bar(B_PFULL), PAIR_SOFTMAX_WARPS);
-        mbar_init(bar(B_PEMPTY), N_PV);
-        mbar_init(bar(B_OFULL), N_PV);
-        mbar_init(bar(B_SYNCA0), PAIR_SOFTMAX_WARPS);
-        mbar_init(bar(B_SYNCA1), PAIR_SOFTMAX_WARPS);
-        mbar_init(bar(B_SYNCB0), PAIR_SOFTMAX_WARPS);
-        mbar_init(bar(B_SYNCB1), PAIR_SOFTMAX_WARPS);
+    // one barrier per thread of warp 0 (31 of them): initialised in one step instead of 31 by a single thread
+    if (warp == 0) {
+        if (lane == 0) {
+            *abort_flag = 0;
+            need_flag[0] = need_flag[1] = 0;
+        }
+        if (lane < B_COUNT) {
+            const int i = int(lane);
+            const uint32_t count = i == B_QFULL ? 1u
+                                 : i == B_QEMPTY ? uint32_t(N_QK)
+                                 : i < B_KEMPTY ? 1u                                                          // KFULL
+                                 : i < B_VFULL ? uint32_t(min(N_QK, NSUB - N_QK * (i - B_KEMPTY)))           // KEMPTY rounds
+                                 : i < B_VEMPTY ? 1u                                                          // VFULL
+                                 : i < B_SFULL ? uint32_t(N_PV)                                               // VEMPTY
+                                 : i == B_SFULL ? uint32_t(N_QK)
+                                 : (i == B_PEMPTY || i == B_OFULL) ? uint32_t(N_PV)
+                                 : uint32_t(PAIR_SOFTMAX_WARPS);                    // SEMPTY, PFULL, SYNCA0/1, SYNCB0/1
+            mbar_init(bar(i), count);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
+    static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -293,6 +296,16 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
                         }
                     }
                 }
+            }
+            // This thread's loads are all issued about a tile before the block finishes.  The next kernel but one of
+            // the stream (the following layer's absorb) starts by streaming that layer's W_UK from HBM; pulling this
+            // block's share of it towards L2 now turns that stream into L2 hits (the bytes move while the last tiles
+            // compute and the partial states are merged).  Any thread of the grid could do it; this one is idle.
+            if (next_weights != nullptr) {
+                const uint32_t nblk = gridDim.x * gridDim.y, me = blockIdx.y * gridDim.x + blockIdx.x;
+                const uint32_t share = ((next_weights_bytes + nblk - 1) / nblk + 15u) & ~15u;
+                const uint32_t off = me * share;
+                if (off < next_weights_bytes) bulk_prefetch_l2(next_weights + off, min(share, next_weights_bytes - off) & ~15u);
             }
         }
     } else if (warp <= N_QK + N_PV) {
@@ -637,8 +650,8 @@ int decode_tc5_pair128_configure()
 // tmaps: the context's tensor-map array (kMapPoolSub = one K sub-tile, kMapPoolV = V boxes, kMapQueries = Q').
 // layer_pool: the layer's slice of the cache pool (linear L2 prefetch).
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
-                              const StepMeta& m, float* recs, uint32_t H, uint32_t prefetch_tiles, uint32_t* status,
-                              cudaStream_t st)
+                              const StepMeta& m, float* recs, uint32_t H, uint32_t prefetch_tiles, const void* next_weights,
+                              uint32_t next_weights_bytes, uint32_t* status, cudaStream_t st)
 {
     if (m.ctas == 0) return 0;
     const CUtensorMap* maps = static_cast<const CUtensorMap*>(tmaps);
@@ -646,9 +659,11 @@ int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_po
     dim3 grid(2 * m.ctas, (H + 2 * HG - 1) / (2 * HG));          // clusters of 2 along x
     if (dtype == 0)
         return int(launch_pdl(decode_tc5_pair128_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV], maps[kMapQueries],
-                              static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles, status));
+                              static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles,
+                              static_cast<const unsigned char*>(next_weights), next_weights_bytes, status));
     return int(launch_pdl(decode_tc5_pair128_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolSub], maps[kMapPoolV],
-                          maps[kMapQueries], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles, status));
+                          maps[kMapQueries], static_cast<const unsigned char*>(layer_pool), layer, n_pages, m, recs, H, scale_log2, prefetch_tiles,
+                              static_cast<const unsigned char*>(next_weights), next_weights_bytes, status));
 }
 
 }  // namespace mla

@@ -43,8 +43,8 @@ enum : int {
 // MMA series): grid (2 x persistent pairs, ceil(H/128)).  Uses kMapPoolSub, kMapPoolV, kMapQueries and the
 // layer's pool slice.
 int launch_decode_tc5_pair128(int dtype, const void* tmaps, const void* layer_pool, uint32_t layer, uint32_t n_pages,
-                              const StepMeta& m, float* recs, uint32_t H, uint32_t prefetch_tiles, uint32_t* status,
-                              cudaStream_t st);
+                              const StepMeta& m, float* recs, uint32_t H, uint32_t prefetch_tiles, const void* next_weights,
+                              uint32_t next_weights_bytes, uint32_t* status, cudaStream_t st);
 int decode_tc5_pair128_configure();
 
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
