@@ -20,6 +20,7 @@ configurations of the workload family, each measured in a few seconds on a handf
   ragged    128 decode rows with log-uniform lengths 256..32768 (1 GPU): step time, planner balance
   v2lite    16 heads, 27 layers, batch 32, ctx 8192, fp16 (1 GPU): whole-step and attention-kernel fractions
   prefill   4 sequences x one 4096-token chunk, causal (1 GPU)
+  verify    speculative-decode verify of K+1 = 5 positions per sequence with rollback, batch 64 (1 GPU)
 (--no-extras skips them.)
 """
 from __future__ import annotations
@@ -685,6 +686,53 @@ def sub_prefill(torch, peak):
     return res
 
 
+def sub_verify(torch, peak):
+    """The reference's speculative-decode verify pass at scale (uspp_scheduler.cpp:550-580, 222-237): per step every
+    sequence verifies K+1 = 5 positions as one small causal chunk, then rolls back to ctx + accepted + 1 rows."""
+    H, L, B, S, K1 = 128, 2, 64, 16384, 5
+    lens = [S - 64] * B
+    ctx, seqs, _, _, _ = _decode_case(torch, lens, H, L, synth.DT_BF16, torch.bfloat16, 515)
+    ctx.close()
+    from mugen_b200.mla import MlaContext
+    pages = sum((n + 64 + 63) // 64 + 1 for n in lens)
+    ctx = MlaContext(n_layers=L, n_heads=H, dtype=synth.DT_BF16, n_pages=pages + 8, max_seqs=B, max_seq_len=S + 128,
+                     max_rows=B * K1, **ROPE_KW)
+    _weights(ctx, L, H, synth.DT_BF16, 515)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(515)
+    seqs = [ctx.seq_create() for _ in range(B)]
+    for l in range(L):
+        for sq, n in zip(seqs, lens):
+            rows = torch.randn((n, 576), device="cuda", dtype=torch.float32, generator=gen).to(torch.bfloat16)
+            ctx.write_rows(l, sq, 0, rows.view(torch.int16))
+    for sq, n in zip(seqs, lens):
+        ctx.advance_seq_len(sq, n)
+    R = B * K1
+    q = (torch.randn((L, R, H, 192), device="cuda", dtype=torch.float32, generator=gen) * 0.9).to(torch.bfloat16).view(torch.int16)
+    kv = torch.randn((L, R, 576), device="cuda", dtype=torch.float32, generator=gen).to(torch.bfloat16).view(torch.int16)
+    out = torch.zeros((L, R, H, 128), device="cuda", dtype=torch.int16)
+    rng = np.random.default_rng(5)
+    cur = list(lens)
+
+    def step():
+        ctx.step_begin(seqs, [K1] * B)
+        ctx.step_layers(0, L, kv, q, out)
+        ctx.step_end()
+        acc = rng.integers(0, K1, B)
+        for b in range(B):
+            cur[b] = min(cur[b] + int(acc[b]) + 1, S - K1)
+        ctx.rollback(seqs, cur)
+    ms = _time_steps(torch, step, 2, 4)
+    assert ctx.status() == 0
+    ctx.close()
+    us_layer = ms * 1e3 / L
+    return {"workload": f"speculative verify: batch {B}, ctx ~{S}, K+1 = {K1} positions per sequence per step, rollback to "
+                        f"ctx + accepted + 1 after every step, 128 heads, bf16, {L} layers timed",
+            "us_per_layer_step": us_layer, "verified_positions_per_s_61_layers_scaled": R / (us_layer * 61e-6),
+            "latent_kv_gbs": R * S * 1152.0 / (us_layer * 1e-6) / 1e9,
+            "note": "every verified position is a query row that streams its sequence's cache: K+1 times the bytes of a decode step"}
+
+
 def run_extras(a, world, rank, local, only=""):
     import torch
     import torch.distributed as dist
@@ -707,6 +755,8 @@ def run_extras(a, world, rank, local, only=""):
             guarded("v2lite", lambda: sub_v2lite(torch, peak))
         if only in ("", "prefill"):
             guarded("prefill", lambda: sub_prefill(torch, peak))
+        if only in ("", "verify"):
+            guarded("verify", lambda: sub_verify(torch, peak))
     return res
 
 

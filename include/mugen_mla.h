@@ -115,6 +115,13 @@ int mla_advance(mla_ctx* ctx, uint32_t seq_id, uint32_t n);
 /* KVCache::truncate (kv_cache.cpp:313-321): frees whole pages past new_len, keeps stale rows
  * inside the last page.  Unlike the reference it never grows: new_len > seq_len is an error. */
 int mla_truncate(mla_ctx* ctx, uint32_t seq_id, uint32_t new_len);
+/* The rollback of a speculative-decode step for many sequences at once (reference: USPPScheduler::decode_step,
+ * src/core/scheduler/uspp_scheduler.cpp:222-237, and the CLI loop, src/cli/main.cpp:658-684): the verify pass
+ * appended K+1 rows per sequence (a step with n_new = K+1); of these only the accepted ones stay.  For every listed
+ * sequence whose seq_len exceeds keep_lens[i] the length is cut to keep_lens[i] (whole pages past it go back to
+ * the pool); a sequence already at or below its keep length is left alone, as the reference's guard
+ * `seq_len() > keep_len` does.  All-or-nothing: unknown ids are reported before anything is cut. */
+int mla_rollback(mla_ctx* ctx, uint32_t n_seq, const uint32_t* seq_ids, const uint32_t* keep_lens);
 /* KVCache::clear (kv_cache.cpp:343-353): returns every page of the sequence. */
 int mla_clear(mla_ctx* ctx, uint32_t seq_id);
 /* Global position of the sequence's local row 0 (default 0).  A KV-range shard of a long

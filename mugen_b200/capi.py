@@ -62,6 +62,7 @@ SIGNATURES = {
     "mla_kernel_name": (C.c_char_p, [vp]),
     "mla_set_q_rope": (C.c_int, [vp, C.c_int]),
     "mla_profile_enable": (C.c_int, [vp, C.c_int]),
+    "mla_rollback": (C.c_int, [vp, u32, vp, vp]),
     "mla_step_balance": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
     "mla_selftest_wait_timeout": (C.c_int, [vp, C.c_uint64, vp, C.POINTER(u32)]),
     "mla_profile_read": (C.c_int, [vp, C.POINTER(u32), C.POINTER(f32)]),

@@ -717,6 +717,17 @@ int mla_truncate(mla_ctx* c, uint32_t id, uint32_t n)
     if (c->in_step) return refuse_in_step(c, "truncate");
     return pt_code(c, c->pt->truncate(id, n));
 }
+int mla_rollback(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const uint32_t* keep_lens)
+{
+    if (!c || (n_seq && (!seq_ids || !keep_lens))) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (c->in_step) return refuse_in_step(c, "rollback");
+    for (uint32_t i = 0; i < n_seq; i++)
+        if (!c->pt->seq(seq_ids[i])) return fail(c, MLA_ERR_INVALID, "unknown sequence id " + std::to_string(seq_ids[i]));
+    for (uint32_t i = 0; i < n_seq; i++)
+        if (c->pt->seq(seq_ids[i])->len > keep_lens[i])
+            if (int e = pt_code(c, c->pt->truncate(seq_ids[i], keep_lens[i]))) return e;
+    return MLA_OK;
+}
 int mla_clear(mla_ctx* c, uint32_t id)
 {
     if (!c) return MLA_ERR_INVALID;

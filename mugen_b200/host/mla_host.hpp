@@ -103,6 +103,11 @@ public:
     }
     auto advance_seq_len(uint32_t seq, uint32_t n = 1) -> Status { return wrap(mla_advance(h_, seq, n)); }
     auto truncate(uint32_t seq, uint32_t new_len) -> Status { return wrap(mla_truncate(h_, seq, new_len)); }
+    // rollback of a speculative verify step for many sequences (uspp_scheduler.cpp:222-237)
+    auto rollback(const std::vector<uint32_t>& seqs, const std::vector<uint32_t>& keep_lens) -> Status {
+        if (seqs.size() != keep_lens.size()) return std::unexpected("rollback: one keep length per sequence");
+        return wrap(mla_rollback(h_, uint32_t(seqs.size()), seqs.data(), keep_lens.data()));
+    }
     auto clear(uint32_t seq) -> Status { return wrap(mla_clear(h_, seq)); }
     auto set_base_position(uint32_t seq, uint32_t base) -> Status { return wrap(mla_seq_set_base(h_, seq, base)); }
     auto config() const -> const LatentKVCacheConfig& { return cfg_; }

@@ -95,6 +95,12 @@ class MlaContext:
     def advance_seq_len(self, seq: int, n: int = 1) -> None:
         self._check(self.lib.mla_advance(self.h, seq, n))
 
+    def rollback(self, seq_ids, keep_lens) -> None:
+        """Speculative-decode rollback for many sequences: cut every listed sequence longer than its keep length
+        (uspp_scheduler.cpp:222-237)."""
+        s, k = _u32(seq_ids), _u32(keep_lens)
+        self._check(self.lib.mla_rollback(self.h, len(s), _np_ptr(s), _np_ptr(k)))
+
     def truncate(self, seq: int, new_len: int) -> None:
         self._check(self.lib.mla_truncate(self.h, seq, new_len))
 

@@ -277,3 +277,70 @@ def test_config5_at_size_ragged_decode_rows_and_four_4096_token_chunks_in_one_st
         want = oracle.attention(qh[b, :hs].copy(), full, dec_lens[b] + 1, wk[:hs * 128], wv[:hs * 128], synth.W_BF16, hs, DT)
         _close(got[b, :hs], want, f"decode row {b} of length {dec_lens[b] + 1}, heads 0-7")
     ctx.close()
+
+
+def test_speculative_verify_steps_with_rollback_at_batch_64(torch, oracle):
+    """The request-level contract of the reference's speculative decoding at scale (USPPScheduler::decode_step,
+    uspp_scheduler.cpp:176-298; verify :550-580): every step verifies K+1 = 5 positions per sequence as one small
+    causal chunk, then keeps ctx + n_accepted + 1 rows and rolls the rest back (truncate), and the next step appends
+    over the rolled-back rows.  64 sequences of ragged lengths, 128 heads, bf16, 4 steps with seeded acceptance counts.
+    Checked: counters after every rollback; after the last step, for sampled sequences, the surviving cache rows
+    equal the checker's append of the accepted tokens only (rolled-back rows were overwritten or dropped), and the
+    outputs of the last verify chunk match the CPU attention over exactly those rows on 8 heads."""
+    from mugen_b200.mla import MlaContext
+    B, K1, steps = 64, 5, 4
+    rng = np.random.default_rng(99)
+    lens0 = [int(n) for n in synth.ragged_lengths(7, B, 300, 6000)]
+    wk, wv, nw = _weights(9)
+    caches = [_rand_bf16(torch, (n, 576), 900 + i) for i, n in enumerate(lens0)]
+    pages = sum((n + steps * K1 + 63) // 64 + 1 for n in lens0) + 8
+    ctx = MlaContext(n_layers=1, n_heads=H, dtype=DT, n_pages=pages, max_seqs=B, max_seq_len=max(lens0) + steps * K1 + 64,
+                     max_rows=B * K1, kernel=capi.KERNEL_AUTO, **YARN)
+    ctx.shuffle_free_pages(4)
+    ctx.set_layer_weights(0, wk, wv, synth.W_BF16, nw)
+    seqs = []
+    for c_, n in zip(caches, lens0):
+        s = ctx.seq_create()
+        ctx.write_rows(0, s, 0, c_)
+        ctx.advance_seq_len(s, n)
+        seqs.append(s)
+    cur = list(lens0)
+    kept = [[] for _ in range(B)]            # per sequence: (position, kv_a bits) of every row that survived
+    for step in range(steps):
+        kv = _rand_bf16(torch, (B * K1, 576), 2000 + step)
+        q = _rand_bf16(torch, (B * K1, H, 192), 3000 + step, 0.9)
+        out = torch.zeros((B * K1, H, 128), dtype=torch.int16, device="cuda")
+        ctx.step_begin(seqs, [K1] * B)
+        ctx.step_layers(0, 1, kv[None], q[None], out[None])
+        ctx.step_end()
+        assert [ctx.seq_len(s) for s in seqs] == [n + K1 for n in cur]
+        n_acc = rng.integers(0, K1, B)       # accepted drafts 0..K; the re-evaluated token always stays
+        keep = [cur[b] + int(n_acc[b]) + 1 for b in range(B)]
+        ctx.rollback(seqs, keep)
+        assert [ctx.seq_len(s) for s in seqs] == keep
+        kvh = _bits(kv)
+        for b in range(B):
+            for t in range(int(n_acc[b]) + 1):
+                kept[b].append((cur[b] + t, kvh[b * K1 + t]))
+        last = (list(cur), kvh, _bits(q), _bits(out), n_acc.copy())
+        cur = keep
+    assert ctx.status() == 0
+    ctx.rollback(seqs, [n + 10 for n in cur])                    # keep length above seq_len: left alone (the reference's guard)
+    assert [ctx.seq_len(s) for s in seqs] == cur
+    start, kvh, qh, outh, n_acc = last
+    hs = 8
+    for b in (0, 17, int(np.argmax(lens0)), B - 1):
+        pos = [p for p, _ in kept[b]]
+        assert pos == list(range(lens0[b], cur[b]))               # contiguous: rollbacks left no holes
+        want_rows = oracle.append_rows(np.stack([r for _, r in kept[b]]), pos, nw, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, DT)
+        assert np.array_equal(ctx.read_rows(0, seqs[b], lens0[b], cur[b] - lens0[b]), want_rows), f"sequence {b}"
+        # the last verify chunk saw the surviving rows below its start plus its own K+1 appended rows
+        chunk_rows = oracle.append_rows(kvh[b * K1:(b + 1) * K1], list(range(start[b], start[b] + K1)), nw,
+                                        YARN["rms_norm_eps"], 40.0, 4096, 10000.0, DT)
+        below = want_rows[:start[b] - lens0[b]]
+        full = np.concatenate([_bits(caches[b]), below, chunk_rows])
+        for t in (0, K1 - 1):
+            want = oracle.attention(qh[b * K1 + t, :hs].copy(), full, start[b] + t + 1, wk[:hs * 128], wv[:hs * 128],
+                                    synth.W_BF16, hs, DT)
+            _close(outh[b * K1 + t, :hs], want, f"sequence {b}, verify position {t}")
+    ctx.close()
