@@ -232,6 +232,32 @@ int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_be
 int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
                    const void* dev_rows, void* stream);
 
+/* ---- weight ingestion from a GGUF model file --------------------------------------------------------- */
+/* Replaces, for this path, the reference's GGUF loading: the MLA metadata keys (src/core/model/transformer.cpp:
+ * 2951-3011; parser src/model/gguf_parser.cpp:158-330) and the per-layer attn_k_b / attn_v_b tensors or the split
+ * of a merged attn_kv_b whose rows per head are [qk_nope rows | v_head_dim rows] (transformer.cpp:3178-3221);
+ * F32 norm weights become 16-bit at load as in the reference (:2850-2869).  The file is memory-mapped; no CUDA
+ * call is made until mla_gguf_register.  Errors: mla_gguf_last_error() (per thread). */
+typedef struct mla_gguf mla_gguf;
+typedef struct mla_gguf_info {
+    uint32_t n_layers, n_heads, embedding_length, context_length;
+    uint32_t kv_lora_rank, q_lora_rank, qk_nope_head_dim, qk_rope_head_dim, v_head_dim, rope_original_ctx;
+    float rope_theta, rope_scaling_factor, rms_norm_eps;
+} mla_gguf_info;
+int mla_gguf_open(const char* path, mla_gguf** out);
+void mla_gguf_close(mla_gguf* g);
+const char* mla_gguf_last_error(void);
+int mla_gguf_get_info(const mla_gguf* g, mla_gguf_info* info);
+/* Copies the model's shape, RoPE and epsilon fields into cfg (max_seq_len too when it is 0: the file's
+ * context_length, or 8192 as the reference defaults); pool geometry, dtype and kernel stay the caller's. */
+int mla_gguf_fill_config(const mla_gguf* g, mla_config* cfg);
+/* One layer's W_UK and W_UV ((n_heads*128) x 512 each, after the split of a merged tensor) in their MLA_W_*
+ * encoding, as HOST bytes, and optionally its kv_a norm as half bits.  w_uk / w_uv may be NULL to query bytes_each. */
+int mla_gguf_layer_weights(mla_gguf* g, uint32_t layer, void* w_uk, void* w_uv, size_t capacity_each, uint32_t* w_type,
+                           size_t* bytes_each, uint16_t* kv_norm_f16);
+/* mla_set_layer_weights for every layer of the file (ctx_dtype = the context's MLA_DTYPE_*, for the norm weights). */
+int mla_gguf_register(mla_ctx* ctx, mla_gguf* g, uint32_t ctx_dtype);
+
 /* Failure-path self-test (no reference counterpart).  Launches one block whose threads wait on a barrier that
  * nothing completes: after `limit_cycles` SM cycles (e.g. 1,000,000: about half a millisecond) the wait gives up,
  * raises the ST_WAIT_TIMEOUT bit (value 4) in the context's device status word, the block frees its tensor memory

@@ -30,6 +30,13 @@ class MlaConfig(C.Structure):
                 ("device", i32), ("kernel", u32), ("max_position", u32)]
 
 
+class GgufInfo(C.Structure):
+    _fields_ = [(n, u32) for n in ("n_layers", "n_heads", "embedding_length", "context_length", "kv_lora_rank",
+                                   "q_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim",
+                                   "rope_original_ctx")] + [(n, f32) for n in ("rope_theta", "rope_scaling_factor",
+                                                                               "rms_norm_eps")]
+
+
 # name -> (restype, argtypes); must list every symbol include/mugen_mla.h declares
 SIGNATURES = {
     "mla_create": (C.c_int, [C.POINTER(MlaConfig), C.POINTER(vp)]),
@@ -62,6 +69,13 @@ SIGNATURES = {
     "mla_kernel_name": (C.c_char_p, [vp]),
     "mla_set_q_rope": (C.c_int, [vp, C.c_int]),
     "mla_profile_enable": (C.c_int, [vp, C.c_int]),
+    "mla_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "mla_gguf_close": (None, [vp]),
+    "mla_gguf_last_error": (C.c_char_p, []),
+    "mla_gguf_get_info": (C.c_int, [vp, C.POINTER(GgufInfo)]),
+    "mla_gguf_fill_config": (C.c_int, [vp, C.POINTER(MlaConfig)]),
+    "mla_gguf_layer_weights": (C.c_int, [vp, u32, vp, vp, C.c_size_t, C.POINTER(u32), C.POINTER(C.c_size_t), vp]),
+    "mla_gguf_register": (C.c_int, [vp, vp, u32]),
     "mla_rollback": (C.c_int, [vp, u32, vp, vp]),
     "mla_step_balance": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
     "mla_selftest_wait_timeout": (C.c_int, [vp, C.c_uint64, vp, C.POINTER(u32)]),
