@@ -232,6 +232,39 @@ int mla_read_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_be
 int mla_write_rows(mla_ctx* ctx, uint32_t layer, uint32_t seq_id, uint32_t row_begin, uint32_t n,
                    const void* dev_rows, void* stream);
 
+/* ---- the projections around the attention: a whole attention block, hidden in -> hidden out ---------------- */
+/* Replaces steps A-D, F, J and K of the reference's MLA decode driver (src/core/model/transformer.cpp:3849-3929,
+ * 4002-4015; kernels rms_norm, matvec_f16, elementwise_add, src/metal/kernel_sources.h:55-98, 264-312, 357-366):
+ *   hidden2 = RMSNorm(hidden) * attn_norm
+ *   q       = W_q_b . RMSNorm(W_q_a . hidden2) * q_a_norm        (q_lora_rank > 0: DeepSeek-V3)
+ *           = W_q . hidden2                                       (q_lora_rank = 0: V2-Lite)
+ *   kv_a    = W_kv_a_mqa . hidden2                                (feeds the append)
+ *   hidden += W_o . attention output
+ * Every projection stores 16-bit results with float accumulation, as the reference's kernels do.  All weights are
+ * HOST pointers in the context's storage type, row-major as GGUF holds them (one output per row):
+ *   attn_norm [E], q_a [q_lora_rank][E], q_a_norm [q_lora_rank], q_b [n_heads*192][q_lora_rank] (or q [n_heads*192][E]
+ *   with q_lora_rank = 0; unused pointers NULL), kv_a_mqa [576][E], wo [E][n_heads*128]. */
+typedef struct mla_block_weights {
+    uint32_t embedding_length;     /* E, a multiple of 8 */
+    uint32_t q_lora_rank;          /* 0: full q projection */
+    const void* attn_norm;
+    const void* q_a;
+    const void* q_a_norm;
+    const void* q_b;
+    const void* q;
+    const void* kv_a_mqa;
+    const void* wo;
+} mla_block_weights;
+int mla_set_block_weights(mla_ctx* ctx, uint32_t layer, const mla_block_weights* w);
+/* Steps A-D and F for `rows` tokens: hidden DEVICE [rows][E] -> q DEVICE [rows][n_heads][192] (BEFORE its RoPE: pass it
+ * to the attention with mla_set_q_rope(ctx, 1), or rotate it yourself) and kv_a DEVICE [rows][576]. */
+int mla_block_project_in(mla_ctx* ctx, uint32_t layer, uint32_t rows, const void* hidden, void* q, void* kv_a, void* stream);
+/* Steps J and K: hidden DEVICE [rows][E] += W_o . attn_out (DEVICE [rows][n_heads][128]). */
+int mla_block_project_out(mla_ctx* ctx, uint32_t layer, uint32_t rows, const void* attn_out, void* hidden, void* stream);
+/* The whole attention block of one layer for the rows of the open step: project in, append + attend (the kernels of
+ * mla_step_layers), project out; hidden DEVICE [rows][E] is updated in place.  Needs mla_set_q_rope(ctx, 1). */
+int mla_step_block(mla_ctx* ctx, uint32_t layer, void* hidden, void* stream);
+
 /* ---- weight ingestion from a GGUF model file --------------------------------------------------------- */
 /* Replaces, for this path, the reference's GGUF loading: the MLA metadata keys (src/core/model/transformer.cpp:
  * 2951-3011; parser src/model/gguf_parser.cpp:158-330) and the per-layer attn_k_b / attn_v_b tensors or the split

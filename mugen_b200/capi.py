@@ -37,6 +37,11 @@ class GgufInfo(C.Structure):
                                                                                "rms_norm_eps")]
 
 
+class BlockWeights(C.Structure):
+    _fields_ = [("embedding_length", u32), ("q_lora_rank", u32)] + [(n, vp) for n in (
+        "attn_norm", "q_a", "q_a_norm", "q_b", "q", "kv_a_mqa", "wo")]
+
+
 # name -> (restype, argtypes); must list every symbol include/mugen_mla.h declares
 SIGNATURES = {
     "mla_create": (C.c_int, [C.POINTER(MlaConfig), C.POINTER(vp)]),
@@ -69,6 +74,10 @@ SIGNATURES = {
     "mla_kernel_name": (C.c_char_p, [vp]),
     "mla_set_q_rope": (C.c_int, [vp, C.c_int]),
     "mla_profile_enable": (C.c_int, [vp, C.c_int]),
+    "mla_set_block_weights": (C.c_int, [vp, u32, C.POINTER(BlockWeights)]),
+    "mla_block_project_in": (C.c_int, [vp, u32, u32, vp, vp, vp, vp]),
+    "mla_block_project_out": (C.c_int, [vp, u32, u32, vp, vp, vp]),
+    "mla_step_block": (C.c_int, [vp, u32, vp, vp]),
     "mla_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
     "mla_gguf_close": (None, [vp]),
     "mla_gguf_last_error": (C.c_char_p, []),

@@ -51,6 +51,7 @@ struct AppendArgs {          // rows == 0: no append blocks in this launch
     const uint32_t* row_pos;
     const uint64_t* row_slot;
     uint32_t rows;
+    uint32_t wait_first;     // kv_a may be the output of the kernel just before this one in the stream
 };
 
 // One new cache row per 128 threads; every statement mirrors append_kernel (mla_kernels.cu), which
@@ -140,13 +141,15 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
 {
     grid_launch_dependents();
     if (blockIdx.x >= absorb_blocks) {
-        // The append touches nothing that an earlier kernel of the stream still reads or writes: its inputs are the
-        // caller's kv_a, constant tables and the step metadata (uploaded before the step's first kernel), and the
-        // slots it writes belong to this layer's pool, last read by this layer's attention in the PREVIOUS step.  So
-        // it works first and waits last; the wait only keeps "this kernel completes after its predecessors", which
-        // the kernels behind it rely on.
+        // Apart from kv_a the append touches nothing that an earlier kernel of the stream still reads or writes:
+        // constant tables, the step metadata (uploaded before the step's first kernel), and slots of this layer's
+        // pool, last read by this layer's attention in the PREVIOUS step.  Where the host knows that kv_a was complete
+        // before the kernel ahead of this one started (the later layers of a multi-layer call, whose kv_a the caller
+        // handed over with the first layer's), the append works first and waits last; the wait then only keeps "this
+        // kernel completes after its predecessors", which the kernels behind it rely on.
+        if (app.wait_first) grid_dependency_wait();
         append_rows<T>(app, (blockIdx.x - absorb_blocks) * APPEND_ROWS, status);
-        grid_dependency_wait();
+        if (!app.wait_first) grid_dependency_wait();
         return;
     }
     extern __shared__ unsigned char absorb_tc5_smem[];
@@ -292,12 +295,12 @@ int absorb_tc5_configure()
 // last 64 dims of every query head are rotated with the row's position (m.row_pos) before they are stored.
 int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, uint32_t rows, uint32_t H, const void* kv_a,
                       void* layer_pool, uint64_t pool_slots, const void* norm_w, const float* cos_sin, uint32_t cs_rows,
-                      float eps, const StepMeta& m, bool rotate_q, uint32_t* status, cudaStream_t st)
+                      float eps, const StepMeta& m, bool rotate_q, bool append_waits, uint32_t* status, cudaStream_t st)
 {
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
     AppendArgs app{};
-    if (kv_a) app = AppendArgs{kv_a, layer_pool, pool_slots, norm_w, cos_sin, cs_rows, eps, m.row_pos, m.row_slot, m.rows};
+    if (kv_a) app = AppendArgs{kv_a, layer_pool, pool_slots, norm_w, cos_sin, cs_rows, eps, m.row_pos, m.row_slot, m.rows, append_waits ? 1u : 0u};
     const uint32_t absorb_blocks = H * ((rows + MT - 1) / MT);
     const uint32_t append_blocks = (app.rows + APPEND_ROWS - 1) / APPEND_ROWS;
     // append blocks carry the trailing indices; for decode batches all blocks are resident at once (H + rows/4 <= SMs)

@@ -37,6 +37,13 @@ struct LayerW {
     bool has_map = false;
 };
 
+// projection weights of one layer's attention block (mla_set_block_weights), all in the storage type on the device
+struct BlockW {
+    uint32_t embed = 0, q_lora = 0;
+    void *attn_norm = nullptr, *q_a = nullptr, *q_a_norm = nullptr, *q_b = nullptr, *q = nullptr, *kv_a = nullptr, *wo = nullptr;
+    bool set = false;
+};
+
 struct MetaBuf {
     void* host = nullptr;       // pinned
     cudaEvent_t done = nullptr;
@@ -56,6 +63,12 @@ struct mla_ctx {
     char* pool = nullptr;           // [layers][n_pages*64][576] elements
     uint64_t pool_slots = 0;        // token slots per layer
     std::vector<LayerW> layers;
+    std::vector<BlockW> blocks;
+    // workspaces of the block projections, grown on demand: normalised hidden state, q_a, float K-slice partials,
+    // and the block's q / kv_a / attention output when the library owns them (mla_step_block)
+    void *blk_hidden2 = nullptr, *blk_qa = nullptr, *blk_q = nullptr, *blk_kv = nullptr, *blk_out = nullptr;
+    float* blk_partial = nullptr;
+    size_t blk_hidden2_cap = 0, blk_qa_cap = 0, blk_q_cap = 0, blk_kv_cap = 0, blk_out_cap = 0, blk_partial_cap = 0;
     float* cos_sin = nullptr;       // device [max positions][64]
     uint32_t cs_rows = 0;           // positions filled so far
     uint32_t cs_cap = 0;
@@ -341,7 +354,7 @@ int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row
 // absorb -> split-KV attention -> merge (+ W_UV, or export of the merged partial state)
 // With fused_kv_a the absorb launch also appends the step's new rows (the caller then skips run_append).
 int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st,
-               const void* fused_kv_a = nullptr)
+               const void* fused_kv_a = nullptr, bool kv_a_settled = false)
 {
     const mla::StepMeta& m = c->meta;
     if (m.rows == 0) return MLA_OK;
@@ -350,7 +363,7 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     if (lw.has_map) {
         const int ae = mla::launch_absorb_tc5(int(c->cfg.dtype), q, &lw.w_uk_map, c->q_abs, m.rows, H, fused_kv_a,
                                               layer_pool(c, layer), c->pool_slots, lw.norm, c->cos_sin, c->cs_rows,
-                                              c->cfg.rms_norm_eps, m, c->q_rope_in_kernel, c->status_dev, st);
+                                              c->cfg.rms_norm_eps, m, c->q_rope_in_kernel, !kv_a_settled, c->status_dev, st);
         if (ae != 0) return fail(c, MLA_ERR_CUDA, std::string("absorb launch: ") + cudaGetErrorString(cudaError_t(ae)));
     } else {
         if (fused_kv_a) return fail(c, MLA_ERR_STATE, "fused append needs the layer's tensor maps");
@@ -381,10 +394,11 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     return MLA_OK;
 }
 
-// one layer of a step: append + attention, with the append riding in the absorb launch where it can
-int run_layer(mla_ctx* c, uint32_t layer, const void* kv_a, const void* q, void* out, cudaStream_t st)
+// one layer of a step: append + attention, with the append riding in the absorb launch where it can.
+// kv_a_settled: kv_a was complete before the kernel launched just ahead of this layer's started (see launch_absorb_tc5).
+int run_layer(mla_ctx* c, uint32_t layer, const void* kv_a, const void* q, void* out, cudaStream_t st, bool kv_a_settled = false)
 {
-    if (c->layers[layer].has_map) return run_attend(c, layer, q, out, nullptr, st, kv_a);
+    if (c->layers[layer].has_map) return run_attend(c, layer, q, out, nullptr, st, kv_a, kv_a_settled);
     if (int e = run_append(c, layer, kv_a, st)) return e;
     return run_attend(c, layer, q, out, nullptr, st);
 }
@@ -549,6 +563,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
 
     c->pt = std::make_unique<PageTable>(cfg->page_tokens, cfg->n_pages, cfg->max_seqs, cfg->max_seq_len);
     c->layers.resize(cfg->n_layers);
+    c->blocks.resize(cfg->n_layers);
     c->pool_slots = uint64_t(cfg->n_pages) * cfg->page_tokens;
     const size_t pool_bytes = size_t(cfg->n_layers) * c->pool_slots * mla::kRow * 2;
     CR_TRY(cudaMalloc(&c->pool, pool_bytes));
@@ -587,6 +602,10 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     }
     if (int ce = mla::merge_mma_configure()) {
         cp->err = std::string("mma merge kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
+    }
+    if (int ce = mla::gemm_tc5_configure()) {
+        cp->err = std::string("tcgen05 projection kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
         return bail(MLA_ERR_CUDA);
     }
     if (int ce = mla::absorb_tc5_configure()) {
@@ -636,6 +655,8 @@ void mla_destroy(mla_ctx* c)
     if (c->h_in) cudaFreeHost(c->h_in);
     if (c->h_out) cudaFreeHost(c->h_out);
     cudaFree(c->d_kv); cudaFree(c->d_q); cudaFree(c->d_out);
+    for (auto& b : c->blocks) { cudaFree(b.attn_norm); cudaFree(b.q_a); cudaFree(b.q_a_norm); cudaFree(b.q_b); cudaFree(b.q); cudaFree(b.kv_a); cudaFree(b.wo); }
+    cudaFree(c->blk_hidden2); cudaFree(c->blk_qa); cudaFree(c->blk_q); cudaFree(c->blk_kv); cudaFree(c->blk_out); cudaFree(c->blk_partial);
     for (auto& ev : c->host_ev) { cudaEventDestroy(ev.in); cudaEventDestroy(ev.compute); cudaEventDestroy(ev.out); }
     if (c->copy_in) cudaStreamDestroy(c->copy_in);
     if (c->copy_out) cudaStreamDestroy(c->copy_out);
@@ -892,7 +913,10 @@ int mla_step_layers(mla_ctx* c, uint32_t layer_begin, uint32_t n_layers, const v
     for (uint32_t i = 0; i < n_layers; i++) {
         const uint32_t layer = layer_begin + i;
         if (int e = check_layer(c, layer, true)) return e;
-        if (int e = run_layer(c, layer, static_cast<const char*>(kv_a) + i * kv_b, static_cast<const char*>(q) + i * q_b, static_cast<char*>(out) + i * o_b, st))
+        // the caller's kv_a for ALL layers existed before this call: from the second layer on, the kernel ahead of the
+        // layer's first launch is this library's own and kv_a was complete before it started
+        if (int e = run_layer(c, layer, static_cast<const char*>(kv_a) + i * kv_b, static_cast<const char*>(q) + i * q_b,
+                              static_cast<char*>(out) + i * o_b, st, i > 0))
             return e;
     }
     return MLA_OK;
@@ -1154,6 +1178,147 @@ int mla_write_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, 
     c->launches += n ? 1 : 0;
     CU_TRY(c, cudaGetLastError());
     return MLA_OK;
+}
+
+}  // extern "C"
+
+// ---- attention block: the projections around the op -----------------------------------------------------------
+namespace {
+
+int grow(mla_ctx* c, void** p, size_t* cap, size_t bytes)
+{
+    if (bytes <= *cap) return MLA_OK;
+    CU_TRY(c, cudaDeviceSynchronize());          // an earlier launch may still use the smaller buffer
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    CU_TRY(c, cudaMalloc(p, bytes));
+    *cap = bytes;
+    return MLA_OK;
+}
+
+// out[rows][N] = act[rows][K] . W[N][K]^T, rounded to the storage type, then `mode` (0 store, 1 RMSNorm(w), 2 += res)
+int project(mla_ctx* c, const void* act, const void* W, uint32_t rows, uint32_t N, uint32_t K, int mode, const void* w,
+            const void* res, void* out, cudaStream_t st)
+{
+    uint32_t splits = mla::gemm_tc5_splits(rows, N, K, uint32_t(c->sm_count));
+    const bool direct = splits == 1 && mode == 0;
+    if (!direct)
+        if (int e = grow(c, reinterpret_cast<void**>(&c->blk_partial), &c->blk_partial_cap, size_t(splits) * rows * N * sizeof(float))) return e;
+    int rc = mla::launch_gemm_tc5(int(c->cfg.dtype), act, K, W, K, rows, N, K, direct ? out : nullptr,
+                                  direct ? nullptr : c->blk_partial, splits, c->status_dev, st);
+    if (rc == -1) return fail(c, MLA_ERR_INVALID, "projection operands must be 16-byte aligned with row lengths that are multiples of 8");
+    if (rc != 0) return fail(c, MLA_ERR_CUDA, std::string("projection launch: ") + cudaGetErrorString(cudaError_t(rc)));
+    c->launches++;
+    if (!direct) {
+        rc = mla::launch_gemm_finalize(int(c->cfg.dtype), c->blk_partial, splits, rows, N, mode, w, c->cfg.rms_norm_eps, res, out, st);
+        if (rc != 0) return fail(c, MLA_ERR_CUDA, std::string("projection finalize launch: ") + cudaGetErrorString(cudaError_t(rc)));
+        c->launches++;
+    }
+    return MLA_OK;
+}
+
+int block_of(mla_ctx* c, uint32_t layer, const BlockW** out)
+{
+    if (layer >= c->cfg.n_layers) return fail(c, MLA_ERR_INVALID, "layer " + std::to_string(layer) + " out of range");
+    if (!c->blocks[layer].set) return fail(c, MLA_ERR_STATE, "block weights of layer " + std::to_string(layer) + " were never registered");
+    *out = &c->blocks[layer];
+    return MLA_OK;
+}
+
+int project_in(mla_ctx* c, const BlockW& b, uint32_t rows, const void* hidden, void* q, void* kv_a, cudaStream_t st)
+{
+    const uint32_t E = b.embed, H = c->cfg.n_heads, QD = H * uint32_t(mla::kQDim);
+    if (int e = grow(c, &c->blk_hidden2, &c->blk_hidden2_cap, size_t(rows) * E * 2)) return e;
+    if (int rc = mla::launch_rmsnorm_rows(int(c->cfg.dtype), hidden, b.attn_norm, c->blk_hidden2, rows, E, c->cfg.rms_norm_eps, st))
+        return fail(c, MLA_ERR_CUDA, std::string("rmsnorm launch: ") + cudaGetErrorString(cudaError_t(rc)));
+    c->launches++;
+    if (b.q_lora) {
+        if (int e = grow(c, &c->blk_qa, &c->blk_qa_cap, size_t(rows) * b.q_lora * 2)) return e;
+        if (int e = project(c, c->blk_hidden2, b.q_a, rows, b.q_lora, E, 1, b.q_a_norm, nullptr, c->blk_qa, st)) return e;
+        if (int e = project(c, c->blk_qa, b.q_b, rows, QD, b.q_lora, 0, nullptr, nullptr, q, st)) return e;
+    } else {
+        if (int e = project(c, c->blk_hidden2, b.q, rows, QD, E, 0, nullptr, nullptr, q, st)) return e;
+    }
+    return project(c, c->blk_hidden2, b.kv_a, rows, uint32_t(mla::kRow), E, 0, nullptr, nullptr, kv_a, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mla_set_block_weights(mla_ctx* c, uint32_t layer, const mla_block_weights* w)
+{
+    if (!c || !w) return fail(c, MLA_ERR_INVALID, "null argument");
+    if (layer >= c->cfg.n_layers) return fail(c, MLA_ERR_INVALID, "layer " + std::to_string(layer) + " out of range");
+    USE_DEVICE(c);
+    const uint32_t E = w->embedding_length, R = w->q_lora_rank, H = c->cfg.n_heads;
+    if (E == 0 || E % 8 || R % 8) return fail(c, MLA_ERR_INVALID, "embedding_length and q_lora_rank must be multiples of 8");
+    if (!w->attn_norm || !w->kv_a_mqa || !w->wo || (R ? (!w->q_a || !w->q_a_norm || !w->q_b) : !w->q))
+        return fail(c, MLA_ERR_INVALID, "missing projection weight for this q_lora_rank");
+    BlockW& b = c->blocks[layer];
+    auto put = [&](void** dst, const void* src, size_t n) -> int {
+        if (*dst) { cudaFree(*dst); *dst = nullptr; }
+        if (!src) return MLA_OK;
+        CU_TRY(c, cudaMalloc(dst, n * 2));
+        CU_TRY(c, cudaMemcpy(*dst, src, n * 2, cudaMemcpyHostToDevice));
+        return MLA_OK;
+    };
+    b.set = false;
+    if (int e = put(&b.attn_norm, w->attn_norm, E)) return e;
+    if (int e = put(&b.q_a, R ? w->q_a : nullptr, size_t(R) * E)) return e;
+    if (int e = put(&b.q_a_norm, R ? w->q_a_norm : nullptr, R)) return e;
+    if (int e = put(&b.q_b, R ? w->q_b : nullptr, size_t(H) * mla::kQDim * R)) return e;
+    if (int e = put(&b.q, R ? nullptr : w->q, size_t(H) * mla::kQDim * E)) return e;
+    if (int e = put(&b.kv_a, w->kv_a_mqa, size_t(mla::kRow) * E)) return e;
+    if (int e = put(&b.wo, w->wo, size_t(E) * H * mla::kVDim)) return e;
+    b.embed = E;
+    b.q_lora = R;
+    b.set = true;
+    return MLA_OK;
+}
+
+int mla_block_project_in(mla_ctx* c, uint32_t layer, uint32_t rows, const void* hidden, void* q, void* kv_a, void* stream)
+{
+    if (!c || (rows && (!hidden || !q || !kv_a))) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
+    const BlockW* b = nullptr;
+    if (int e = block_of(c, layer, &b)) return e;
+    if (rows == 0) return MLA_OK;
+    return project_in(c, *b, rows, hidden, q, kv_a, static_cast<cudaStream_t>(stream));
+}
+
+int mla_block_project_out(mla_ctx* c, uint32_t layer, uint32_t rows, const void* attn_out, void* hidden, void* stream)
+{
+    if (!c || (rows && (!attn_out || !hidden))) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
+    const BlockW* b = nullptr;
+    if (int e = block_of(c, layer, &b)) return e;
+    if (rows == 0) return MLA_OK;
+    // hidden = hidden + W_o . attn_out: the residual is read and the sum written by the finalize kernel
+    return project(c, attn_out, b->wo, rows, b->embed, c->cfg.n_heads * uint32_t(mla::kVDim), 2, nullptr, hidden, hidden,
+                   static_cast<cudaStream_t>(stream));
+}
+
+int mla_step_block(mla_ctx* c, uint32_t layer, void* hidden, void* stream)
+{
+    if (!c || !hidden) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_block outside step_begin/step_end");
+    if (!c->q_rope_in_kernel)
+        return fail(c, MLA_ERR_STATE, "the block's q projection is not rotated: enable mla_set_q_rope(ctx, 1) first");
+    if (int e = check_layer(c, layer, true)) return e;
+    const BlockW* b = nullptr;
+    if (int e = block_of(c, layer, &b)) return e;
+    auto st = static_cast<cudaStream_t>(stream);
+    const uint32_t rows = c->meta.rows, H = c->cfg.n_heads;
+    if (rows == 0) return MLA_OK;
+    if (int e = grow(c, &c->blk_q, &c->blk_q_cap, size_t(rows) * H * mla::kQDim * 2)) return e;
+    if (int e = grow(c, &c->blk_kv, &c->blk_kv_cap, size_t(rows) * mla::kRow * 2)) return e;
+    if (int e = grow(c, &c->blk_out, &c->blk_out_cap, size_t(rows) * H * mla::kVDim * 2)) return e;
+    if (int e = project_in(c, *b, rows, hidden, c->blk_q, c->blk_kv, st)) return e;
+    if (int e = run_layer(c, layer, c->blk_kv, c->blk_q, c->blk_out, st)) return e;
+    return project(c, c->blk_out, b->wo, rows, b->embed, H * uint32_t(mla::kVDim), 2, nullptr, hidden, hidden, st);
 }
 
 }  // extern "C"

@@ -55,10 +55,11 @@ int merge_mma_configure();
 // Absorb on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the layer's W_UK^T,
 // [H*512 d][128 i], box 64 i x 256 d, 128-byte swizzle.  With kv_a != nullptr the same launch appends the step's
 // new rows (launch_append's arguments) in extra blocks.  rotate_q: q arrives before its RoPE; the kernel rotates
-// the last 64 dims of every head with the row's position (m.row_pos) and the cos/sin table.
+// the last 64 dims of every head with the row's position (m.row_pos) and the cos/sin table.  append_waits: kv_a may
+// have been written by the kernel launched just before this one (the append blocks then wait for it before reading).
 int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, uint32_t rows, uint32_t H, const void* kv_a,
                       void* layer_pool, uint64_t pool_slots, const void* norm_w, const float* cos_sin, uint32_t cs_rows,
-                      float eps, const StepMeta& m, bool rotate_q, uint32_t* status, cudaStream_t st);
+                      float eps, const StepMeta& m, bool rotate_q, bool append_waits, uint32_t* status, cudaStream_t st);
 int absorb_tc5_configure();
 
 // The same merge + projection on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the
@@ -66,6 +67,18 @@ int absorb_tc5_configure();
 int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, const void* w_map,
                      void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st);
 int merge_tc5_configure();
+
+// Dense projection C = A . W^T on tcgen05 (mla_gemm_tc5.cu).  A [M][K] pitch lda, W [N][K] pitch ldw (the reference's
+// matvec weight layout), 16-bit DEVICE operands.  partial == nullptr: C in the storage type to `out`; else float
+// partials [splits][M][N] to be finished by launch_gemm_finalize (mode 0 store, 1 RMSNorm with w / eps, 2 residual
+// add of res).  Return: cudaError_t value, or -1 when a tensor map cannot be built.
+int launch_gemm_tc5(int dtype, const void* A, uint32_t lda, const void* W, uint32_t ldw, uint32_t M, uint32_t N, uint32_t K,
+                    void* out, float* partial, uint32_t splits, uint32_t* status, cudaStream_t st);
+int launch_gemm_finalize(int dtype, const float* partial, uint32_t splits, uint32_t M, uint32_t N, int mode, const void* w,
+                         float eps, const void* res, void* out, cudaStream_t st);
+int launch_rmsnorm_rows(int dtype, const void* x, const void* w, void* y, uint32_t rows, uint32_t N, float eps, cudaStream_t st);
+uint32_t gemm_tc5_splits(uint32_t M, uint32_t N, uint32_t K, uint32_t sm_count);   // K slices that fill the SMs once
+int gemm_tc5_configure();
 
 // One block that waits `limit_cycles` on a barrier nothing completes, raises ST_WAIT_TIMEOUT in *status, frees its
 // tensor memory and returns; report[0] = 0 when the wait gave up, report[1] = cycles waited.

@@ -95,6 +95,27 @@ class MlaContext:
     def advance_seq_len(self, seq: int, n: int = 1) -> None:
         self._check(self.lib.mla_advance(self.h, seq, n))
 
+    # ---- the projections around the op (steps A-D, F, J, K of the decode driver) -------------------
+    def set_block_weights(self, layer: int, *, attn_norm, kv_a_mqa, wo, q=None, q_a=None, q_a_norm=None, q_b=None) -> None:
+        """All arrays: uint16 bit patterns in the context dtype, row-major [outputs][inputs] as GGUF holds them."""
+        arrs = dict(attn_norm=attn_norm, q_a=q_a, q_a_norm=q_a_norm, q_b=q_b, q=q, kv_a_mqa=kv_a_mqa, wo=wo)
+        arrs = {k: (None if v is None else np.ascontiguousarray(v, np.uint16)) for k, v in arrs.items()}
+        w = capi.BlockWeights(int(arrs["attn_norm"].size), 0 if q_a is None else int(arrs["q_a"].shape[0]),
+                              *[None if arrs[k] is None else _np_ptr(arrs[k]) for k in
+                                ("attn_norm", "q_a", "q_a_norm", "q_b", "q", "kv_a_mqa", "wo")])
+        self._check(self.lib.mla_set_block_weights(self.h, layer, C.byref(w)))
+
+    def block_project_in(self, layer: int, hidden, q, kv_a) -> None:
+        self._check(self.lib.mla_block_project_in(self.h, layer, hidden.shape[0], self._dev(hidden), self._dev(q),
+                                                  self._dev(kv_a), self._stream()))
+
+    def block_project_out(self, layer: int, attn_out, hidden) -> None:
+        self._check(self.lib.mla_block_project_out(self.h, layer, hidden.shape[0], self._dev(attn_out), self._dev(hidden),
+                                                   self._stream()))
+
+    def step_block(self, layer: int, hidden) -> None:
+        self._check(self.lib.mla_step_block(self.h, layer, self._dev(hidden), self._stream()))
+
     def rollback(self, seq_ids, keep_lens) -> None:
         """Speculative-decode rollback for many sequences: cut every listed sequence longer than its keep length
         (uspp_scheduler.cpp:222-237)."""

@@ -31,6 +31,13 @@ from oracle import binding  # noqa: E402
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import tiny_gguf  # noqa: E402
 
+# A still smaller model whose every decode call is recorded in full (the "block" entries): what the reference's decode
+# driver fed into and got out of each layer's attention block, position by position.  The projections inside it run on
+# the harness's C++ restatements of the reference's Metal kernels (the shaders cannot run on this host); RMSNorm of
+# kv_a, both RoPEs, the attention and the order of the steps are the reference's own host code.
+BLOCK_CASE = dict(name="C: block trace, q-LoRA", model=dict(n_heads=2, embed=64, q_lora_rank=32, ffn=32, vocab=8, seed=13,
+                                                          context_length=64), positions=10)
+
 # Tiny models driven through the reference's forward(); `steps` = (token, position) calls in order, `keep` =
 # the positions whose rows are stored.  The reference writes the row at the caller's position without checking
 # that it equals seq_len (src/core/model/transformer.cpp:3982), so model B may jump.
@@ -138,6 +145,15 @@ def main() -> None:
                                       "q_in": b64(taps["q_pre"][0]), "q_out": b64(taps["q_post"][0]),
                                       "source": "reference forward(), step E"})
             mod.close()
+        path = os.path.join(tmp, "block.gguf")
+        tiny_gguf.write(path, tiny_gguf.TinyModel(**BLOCK_CASE["model"]))
+        mod = ref.load_model(path)
+        out["block"] = {"model": BLOCK_CASE["model"], "name": BLOCK_CASE["name"], "steps": [],
+                        "source": "reference forward() on host restatements of its Metal kernels"}
+        for pos in range(BLOCK_CASE["positions"]):
+            taps = mod.forward(pos % BLOCK_CASE["model"]["vocab"], pos)
+            out["block"]["steps"].append({k: b64(v) for k, v in taps.items()})
+        mod.close()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mla_golden.json")
     with open(path, "w") as f:
         json.dump(out, f, indent=1)
