@@ -137,7 +137,8 @@ template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict__ q, T* __restrict__ q_abs, uint32_t rows,
                   uint32_t H, uint32_t absorb_blocks, const AppendArgs app, const float* __restrict__ q_cos_sin,
-                  const uint32_t* __restrict__ q_pos, uint32_t cs_rows, uint32_t* __restrict__ status)
+                  const uint32_t* __restrict__ q_pos, const uint32_t* __restrict__ att_row, uint32_t cs_rows,
+                  uint32_t* __restrict__ status)
 {
     grid_launch_dependents();
     if (blockIdx.x >= absorb_blocks) {
@@ -185,7 +186,7 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
     for (uint32_t c = tid; c < MT * 16; c += NUM_THREADS) {                 // 16 chunks of 16 bytes per row
         const uint32_t rr = c / 16, ch = c % 16, r = r0 + rr;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows) v = reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim)[ch];
+        if (r < rows) v = reinterpret_cast<const uint4*>(q + (size_t(att_row ? att_row[r] : r) * H + h) * kQDim)[ch];
         *reinterpret_cast<uint4*>(sm + OFF_A + (ch / 8) * A_SUB + rr * 128 + (((ch % 8) ^ (rr & 7)) << 4)) = v;
     }
     if (q_cos_sin == nullptr) {
@@ -193,7 +194,7 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
             const uint32_t rr = c / 8, ch = c % 8, r = r0 + rr;
             if (r < rows)
                 reinterpret_cast<uint4*>(q_abs + (size_t(r) * H + h) * kRow + kRank)[ch] =
-                    reinterpret_cast<const uint4*>(q + (size_t(r) * H + h) * kQDim + kNope)[ch];
+                    reinterpret_cast<const uint4*>(q + (size_t(att_row ? att_row[r] : r) * H + h) * kQDim + kNope)[ch];
         }
     } else {
         // q-side RoPE (reference: transformer.cpp:3882-3921, NeoX pairs (i, i+32), YaRN frequencies): the same
@@ -206,7 +207,7 @@ absorb_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const T* __restrict
                 if (i == 0) atomicOr(status, ST_BAD_SLOT);
                 continue;
             }
-            const T* src = q + (size_t(r) * H + h) * kQDim + kNope;
+            const T* src = q + (size_t(att_row ? att_row[r] : r) * H + h) * kQDim + kNope;
             T* dst = q_abs + (size_t(r) * H + h) * kRow + kRank;
             const float cs = q_cos_sin[size_t(pos) * kRope + i], sn = q_cos_sin[size_t(pos) * kRope + 32 + i];
             const float x0 = Elem<T>::to_f32(src[i]), x1 = Elem<T>::to_f32(src[32 + i]);
@@ -300,17 +301,17 @@ int launch_absorb_tc5(int dtype, const void* q, const void* w_map, void* q_abs, 
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
     AppendArgs app{};
-    if (kv_a) app = AppendArgs{kv_a, layer_pool, pool_slots, norm_w, cos_sin, cs_rows, eps, m.row_pos, m.row_slot, m.rows, append_waits ? 1u : 0u};
+    if (kv_a) app = AppendArgs{kv_a, layer_pool, pool_slots, norm_w, cos_sin, cs_rows, eps, m.app_pos, m.app_slot, m.app_rows, append_waits ? 1u : 0u};
     const uint32_t absorb_blocks = H * ((rows + MT - 1) / MT);
     const uint32_t append_blocks = (app.rows + APPEND_ROWS - 1) / APPEND_ROWS;
     // append blocks carry the trailing indices; for decode batches all blocks are resident at once (H + rows/4 <= SMs)
     dim3 grid(absorb_blocks + append_blocks);
     if (dtype == 0)
         return int(launch_pdl(absorb_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, static_cast<const __half*>(q),
-                              static_cast<__half*>(q_abs), rows, H, absorb_blocks, app, rotate_q ? cos_sin : nullptr, m.row_pos, cs_rows, status));
+                              static_cast<__half*>(q_abs), rows, H, absorb_blocks, app, rotate_q ? cos_sin : nullptr, m.row_pos, m.att_row, cs_rows, status));
     return int(launch_pdl(absorb_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map,
                           static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs), rows, H, absorb_blocks, app,
-                          rotate_q ? cos_sin : nullptr, m.row_pos, cs_rows, status));
+                          rotate_q ? cos_sin : nullptr, m.row_pos, m.att_row, cs_rows, status));
 }
 
 }  // namespace mla

@@ -27,6 +27,7 @@ constexpr int kMetaRing = 4;
 
 struct LayerW {
     void* w_uk = nullptr;   // stored transposed per head: [h][512][128]
+    void* w_uk_rows = nullptr;   // as registered, (H*128) x 512: the prefill path expands keys with it
     void* w_uv = nullptr;
     void* norm = nullptr;
     bool set = false;
@@ -87,13 +88,25 @@ struct mla_ctx {
     size_t meta_cap = 0;
     char* meta_dev = nullptr;
     mla::StepMeta meta{};
+    // A step that holds prefill chunks (sequences taking >= kPrefillMin new tokens) has a second plan: its query rows
+    // are the step's OTHER rows, the chunks go through the expanded-form prefill kernels (run_layer).  The explicit
+    // per-layer calls (mla_step_append / _attend / _attend_partial) keep using the first plan, in which every new token
+    // is a decode-style query row.
+    mla::StepMeta meta_b{};
+    bool has_plan_b = false;
+    struct Chunk { uint32_t seq_id, q_row0, n_new, start, base_pos; };
+    std::vector<Chunk> chunks;
+    uint32_t step_rows = 0;          // rows of the step in the caller's q / kv_a / out tensors
+    // prefill workspaces, grown on demand: gathered latent rows, expanded keys and values, rotated chunk queries
+    void *pf_latent = nullptr, *pf_kx = nullptr, *pf_vx = nullptr, *pf_q = nullptr;
+    size_t pf_latent_cap = 0, pf_kx_cap = 0, pf_vx_cap = 0, pf_q_cap = 0;
 
     // pages of the last planned step per persistent worker (mla_step_balance)
     uint32_t plan_workers = 0, plan_min_pages = 0, plan_max_pages = 0;
 
     // step state
     bool in_step = false;
-    std::vector<uint32_t> step_seqs, step_nnew;
+    std::vector<uint32_t> step_seqs, step_nnew, step_tbl_off;
 
     // optional per-launch timing of the attention kernel
     bool q_rope_in_kernel = false;  // queries arrive before their RoPE (mla_set_q_rope)
@@ -219,9 +232,10 @@ struct RowSpec {
     uint64_t slot;        // destination slot (append only)
 };
 
-// Packs the step metadata, uploads it through the pinned ring and points c->meta at it.
+// Packs the step metadata, uploads it through the pinned ring and points c->meta (plan_b: c->meta_b) at it.
+// att_row: for each query row its row in the caller's tensors (plan_b only).
 int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vector<RowSpec>& rows,
-                bool with_segments, cudaStream_t st)
+                bool with_segments, cudaStream_t st, bool plan_b = false, const std::vector<uint32_t>* att_row = nullptr)
 {
     const uint32_t R = uint32_t(rows.size()), S = uint32_t(seq_ids.size());
     std::vector<uint32_t> lens(R);
@@ -266,7 +280,7 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     const size_t o_slot = take(size_t(R) * 8), o_seq = take(size_t(R) * 4), o_len = take(size_t(R) * 4),
                  o_pos = take(size_t(R) * 4), o_tblo = take(size_t(S) * 4), o_tbl = take(tbl_total * 4 + 4),
                  o_sr = take(size_t(G) * 4), o_sb = take(size_t(G) * 4), o_se = take(size_t(G) * 4),
-                 o_rsb = take(size_t(R + 1) * 4), o_csb = take(size_t(W + 1) * 4);
+                 o_rsb = take(size_t(R + 1) * 4), o_csb = take(size_t(W + 1) * 4), o_att = take(att_row ? size_t(R) * 4 : 0);
     if (off > c->meta_cap)
         return fail(c, MLA_ERR_CAPACITY, "step metadata (" + std::to_string(off) + " B) exceeds the buffer (" +
                                              std::to_string(c->meta_cap) + " B)");
@@ -303,12 +317,13 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     }
     std::memcpy(h + o_rsb, row_seg_begin.data(), size_t(R + 1) * 4);
     std::memcpy(h + o_csb, cta_seg_begin.data(), size_t(W + 1) * 4);
-    if (off) CU_TRY(c, cudaMemcpyAsync(c->meta_dev, h, off, cudaMemcpyHostToDevice, st));
+    if (att_row) std::memcpy(h + o_att, att_row->data(), size_t(R) * 4);
+    char* d = c->meta_dev + (plan_b ? c->meta_cap : 0);
+    if (off) CU_TRY(c, cudaMemcpyAsync(d, h, off, cudaMemcpyHostToDevice, st));
     CU_TRY(c, cudaEventRecord(mb.done, st));
     mb.in_flight = true;
 
-    char* d = c->meta_dev;
-    mla::StepMeta& m = c->meta;
+    mla::StepMeta& m = plan_b ? c->meta_b : c->meta;
     m.row_slot = reinterpret_cast<const uint64_t*>(d + o_slot);
     m.row_seq = reinterpret_cast<const uint32_t*>(d + o_seq);
     m.row_len = reinterpret_cast<const uint32_t*>(d + o_len);
@@ -323,6 +338,11 @@ int upload_meta(mla_ctx* c, const std::vector<uint32_t>& seq_ids, const std::vec
     m.rows = R;
     m.segs = G;
     m.ctas = W;
+    // by default the rows to append are the query rows themselves
+    m.app_rows = R;
+    m.app_pos = m.row_pos;
+    m.app_slot = m.row_slot;
+    m.att_row = att_row ? reinterpret_cast<const uint32_t*>(d + o_att) : nullptr;
     return MLA_OK;
 }
 
@@ -343,20 +363,20 @@ int run_append(mla_ctx* c, uint32_t layer, const void* kv_a, cudaStream_t st)
 {
     mla::launch_append(int(c->cfg.dtype), kv_a, layer_pool(c, layer), c->pool_slots, c->layers[layer].norm,
                        c->cos_sin, c->cs_rows, c->cfg.rms_norm_eps, c->meta, c->status_dev, st);
-    c->launches += c->meta.rows ? 1 : 0;
+    c->launches += c->meta.app_rows ? 1 : 0;
     CU_TRY(c, cudaGetLastError());
     return MLA_OK;
 }
 
 int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, void* out,
-              float* exported, uint32_t rows, cudaStream_t st);
+              float* exported, uint32_t rows, cudaStream_t st, const uint32_t* att_row = nullptr);
 
 // absorb -> split-KV attention -> merge (+ W_UV, or export of the merged partial state)
 // With fused_kv_a the absorb launch also appends the step's new rows (the caller then skips run_append).
 int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* exported, cudaStream_t st,
-               const void* fused_kv_a = nullptr, bool kv_a_settled = false)
+               const void* fused_kv_a = nullptr, bool kv_a_settled = false, bool plan_b = false)
 {
-    const mla::StepMeta& m = c->meta;
+    const mla::StepMeta& m = plan_b ? c->meta_b : c->meta;
     if (m.rows == 0) return MLA_OK;
     const uint32_t H = c->cfg.n_heads;
     const LayerW& lw = c->layers[layer];
@@ -368,6 +388,7 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
     } else {
         if (fused_kv_a) return fail(c, MLA_ERR_STATE, "fused append needs the layer's tensor maps");
         if (c->q_rope_in_kernel) return fail(c, MLA_ERR_UNSUPPORTED, "in-kernel q RoPE needs the layer's tensor maps");
+        if (m.att_row) return fail(c, MLA_ERR_UNSUPPORTED, "a step with prefill chunks needs the layer's tensor maps");
         mla::launch_absorb(int(c->cfg.dtype), q, lw.w_uk, c->q_abs, m.rows, H, st);
     }
     int e;
@@ -388,8 +409,70 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
                                    c->recs, H, c->status_dev, st);
     if (e != 0) return fail(c, MLA_ERR_CUDA, std::string("attention launch: ") + cudaGetErrorString(cudaError_t(e)));
     if (timed) CU_TRY(c, cudaEventRecord(c->prof_events[c->prof_used++].second, st));
-    if (int rc = run_merge(c, layer, c->recs, m.row_seg_begin, 0, out, exported, m.rows, st)) return rc;
+    if (int rc = run_merge(c, layer, c->recs, m.row_seg_begin, 0, out, exported, m.rows, st, m.att_row)) return rc;
     c->launches += 3;
+    CU_TRY(c, cudaGetLastError());
+    return MLA_OK;
+}
+
+// Sequences that take at least this many new tokens in a step go through the prefill kernels.
+constexpr uint32_t kPrefillMin = 64;
+
+int grow_buf(mla_ctx* c, void** p, size_t* cap, size_t bytes)
+{
+    if (bytes <= *cap) return MLA_OK;
+    CU_TRY(c, cudaDeviceSynchronize());          // an earlier launch may still use the smaller buffer
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    CU_TRY(c, cudaMalloc(p, bytes + bytes / 4));
+    *cap = bytes + bytes / 4;
+    return MLA_OK;
+}
+
+// The chunks of the open step, one after the other: gather the sequence's latent rows (the chunk's own rows were
+// appended by the launch before), expand them into per-head keys and values with W_UK / W_UV, run causal flash
+// attention of the chunk's queries over them.  Reference semantics: src/core/model/transformer.cpp:1263-1337.
+int run_chunks(mla_ctx* c, uint32_t layer, const void* q, void* out, cudaStream_t st)
+{
+    const uint32_t H = c->cfg.n_heads;
+    const LayerW& lw = c->layers[layer];
+    const int dt = int(c->cfg.dtype);
+    for (const auto& ch : c->chunks) {
+        const uint32_t total = ch.start + ch.n_new;
+        if (int e = grow_buf(c, &c->pf_latent, &c->pf_latent_cap, size_t(total) * mla::kRow * 2)) return e;
+        if (int e = grow_buf(c, &c->pf_kx, &c->pf_kx_cap, size_t(total) * H * mla::kNope * 2)) return e;
+        if (int e = grow_buf(c, &c->pf_vx, &c->pf_vx_cap, size_t(total) * H * mla::kVDim * 2)) return e;
+        // the sequence's block table inside the first plan's upload
+        uint32_t si = 0;
+        for (; si < c->step_seqs.size(); si++) if (c->step_seqs[si] == ch.seq_id) break;
+        const uint32_t* table = c->meta.tables + c->step_tbl_off[si];
+        int rc = mla::launch_gather_rows(layer_pool(c, layer), c->pool_slots, table, total, c->pf_latent, c->status_dev, st);
+        if (rc) return fail(c, MLA_ERR_CUDA, std::string("gather launch: ") + cudaGetErrorString(cudaError_t(rc)));
+        rc = mla::launch_gemm_tc5(dt, c->pf_latent, mla::kRow, lw.w_uk_rows, mla::kRank, total, H * mla::kNope, mla::kRank, c->pf_kx,
+                                  nullptr, 1, c->status_dev, st);
+        if (rc == 0)
+            rc = mla::launch_gemm_tc5(dt, c->pf_latent, mla::kRow, lw.w_uv, mla::kRank, total, H * mla::kVDim, mla::kRank, c->pf_vx,
+                                      nullptr, 1, c->status_dev, st);
+        if (rc) return fail(c, rc == -1 ? MLA_ERR_INVALID : MLA_ERR_CUDA, "key / value expansion launch failed");
+        const void* qp = q;
+        uint32_t q_rows_total = c->step_rows, q_row0 = ch.q_row0;
+        if (c->q_rope_in_kernel) {           // the chunk's queries arrive before their RoPE: rotate a copy
+            if (int e = grow_buf(c, &c->pf_q, &c->pf_q_cap, size_t(ch.n_new) * H * mla::kQDim * 2)) return e;
+            rc = mla::launch_rotate_q_rows(dt, static_cast<const char*>(q) + size_t(ch.q_row0) * H * mla::kQDim * 2, c->pf_q, ch.n_new, H,
+                                           ch.base_pos + ch.start, c->cos_sin, c->cs_rows, c->status_dev, st);
+            if (rc) return fail(c, MLA_ERR_CUDA, std::string("query rotation launch: ") + cudaGetErrorString(cudaError_t(rc)));
+            c->launches++;
+            qp = c->pf_q;
+            q_rows_total = ch.n_new;
+            q_row0 = 0;
+        }
+        // out rows are addressed from the chunk's first row in either case
+        rc = mla::launch_prefill_tc5(dt, qp, q_rows_total, q_row0, ch.n_new, ch.start, c->pf_kx, c->pf_vx, c->pf_latent,
+                                     static_cast<char*>(out) + (size_t(ch.q_row0) - q_row0) * H * mla::kVDim * 2, H, c->status_dev, st);
+        if (rc) return fail(c, rc == -1 ? MLA_ERR_INVALID : MLA_ERR_CUDA, "prefill attention launch failed");
+        c->launches += 4;
+    }
     CU_TRY(c, cudaGetLastError());
     return MLA_OK;
 }
@@ -398,6 +481,15 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
 // kv_a_settled: kv_a was complete before the kernel launched just ahead of this layer's started (see launch_absorb_tc5).
 int run_layer(mla_ctx* c, uint32_t layer, const void* kv_a, const void* q, void* out, cudaStream_t st, bool kv_a_settled = false)
 {
+    if (c->has_plan_b) {
+        // decode-style rows through the second plan (their append covers ALL new rows of the step), then the chunks
+        if (c->meta_b.rows && c->layers[layer].has_map) {
+            if (int e = run_attend(c, layer, q, out, nullptr, st, kv_a, kv_a_settled, true)) return e;
+        } else {
+            if (int e = run_append(c, layer, kv_a, st)) return e;
+        }
+        return run_chunks(c, layer, q, out, st);
+    }
     if (c->layers[layer].has_map) return run_attend(c, layer, q, out, nullptr, st, kv_a, kv_a_settled);
     if (int e = run_append(c, layer, kv_a, st)) return e;
     return run_attend(c, layer, q, out, nullptr, st);
@@ -448,16 +540,16 @@ int make_weight_map(mla_ctx* c, uint32_t layer)
 
 // merge of the partial states + W_UV: tensor-core kernel, or the scalar one when the merged state is exported
 int run_merge(mla_ctx* c, uint32_t layer, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, void* out,
-              float* exported, uint32_t rows, cudaStream_t st)
+              float* exported, uint32_t rows, cudaStream_t st, const uint32_t* att_row)
 {
     const LayerW& lw = c->layers[layer];
     if (!exported && lw.has_map) {
         const int e = mla::launch_merge_tc5(int(c->cfg.dtype), recs, row_seg_begin, n_parts, &lw.w_uv_map, out, rows,
-                                            c->cfg.n_heads, c->status_dev, st);
+                                            c->cfg.n_heads, att_row, c->status_dev, st);
         if (e != 0) return fail(c, MLA_ERR_CUDA, std::string("merge launch: ") + cudaGetErrorString(cudaError_t(e)));
         return MLA_OK;
     }
-    mla::launch_merge(int(c->cfg.dtype), recs, row_seg_begin, n_parts, lw.w_uv, out, exported, rows, c->cfg.n_heads, st);
+    mla::launch_merge(int(c->cfg.dtype), recs, row_seg_begin, n_parts, lw.w_uv, out, exported, rows, c->cfg.n_heads, st, att_row);
     return MLA_OK;
 }
 
@@ -572,6 +664,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     CR_TRY(cudaMemset(c->pool, 0, pool_bytes));
     for (auto& lw : c->layers) {
         CR_TRY(cudaMalloc(&lw.w_uk, size_t(H) * mla::kNope * mla::kRank * 2));
+        CR_TRY(cudaMalloc(&lw.w_uk_rows, size_t(H) * mla::kNope * mla::kRank * 2));
         CR_TRY(cudaMalloc(&lw.w_uv, size_t(H) * mla::kVDim * mla::kRank * 2));
         CR_TRY(cudaMalloc(&lw.norm, mla::kRank * 2));
     }
@@ -590,8 +683,8 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     const size_t tbl_entries = std::min<size_t>(size_t(cfg->max_seqs) * max_pages_per_seq, cfg->n_pages) + 4;
     c->meta_cap = align16(size_t(R) * 8) + 3 * align16(size_t(R) * 4) + align16(size_t(cfg->max_seqs) * 4) +
                   align16(tbl_entries * 4 + 4) + 3 * align16(size_t(c->max_segs) * 4) +
-                  align16(size_t(R + 1) * 4) + align16(size_t(c->workers + 1) * 4) + 256;
-    CR_TRY(cudaMalloc(&c->meta_dev, c->meta_cap));
+                  align16(size_t(R + 1) * 4) + align16(size_t(c->workers + 1) * 4) + align16(size_t(R) * 4) + 256;
+    CR_TRY(cudaMalloc(&c->meta_dev, 2 * c->meta_cap));                // the two plans of a step live side by side
     for (auto& mb : c->ring) {
         CR_TRY(cudaMallocHost(&mb.host, c->meta_cap));
         CR_TRY(cudaEventCreateWithFlags(&mb.done, cudaEventDisableTiming));
@@ -602,6 +695,10 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     }
     if (int ce = mla::merge_mma_configure()) {
         cp->err = std::string("mma merge kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+        return bail(MLA_ERR_CUDA);
+    }
+    if (int ce = mla::prefill_tc5_configure()) {
+        cp->err = std::string("tcgen05 prefill kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
         return bail(MLA_ERR_CUDA);
     }
     if (int ce = mla::gemm_tc5_configure()) {
@@ -641,7 +738,8 @@ void mla_destroy(mla_ctx* c)
     cudaSetDevice(c->cfg.device);
     cudaDeviceSynchronize();
     cudaFree(c->pool);
-    for (auto& lw : c->layers) { cudaFree(lw.w_uk); cudaFree(lw.w_uv); cudaFree(lw.norm); }
+    for (auto& lw : c->layers) { cudaFree(lw.w_uk); cudaFree(lw.w_uk_rows); cudaFree(lw.w_uv); cudaFree(lw.norm); }
+    cudaFree(c->pf_latent); cudaFree(c->pf_kx); cudaFree(c->pf_vx); cudaFree(c->pf_q);
     cudaFree(c->cos_sin);
     cudaFree(c->q_abs);
     cudaFree(c->recs);
@@ -695,6 +793,7 @@ int mla_set_layer_weights(mla_ctx* c, uint32_t layer, const void* w_uk, const vo
                 for (size_t d = 0; d < size_t(mla::kRank); d++)
                     tr[(h * mla::kRank + d) * mla::kNope + i] = buf[(h * mla::kNope + i) * mla::kRank + d];
         CU_TRY(c, cudaMemcpy(c->layers[layer].w_uk, tr.data(), tr.size() * 2, cudaMemcpyHostToDevice));
+        CU_TRY(c, cudaMemcpy(c->layers[layer].w_uk_rows, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
     }
     if (int e = decode_weights(c, w_uv, w_type, H * mla::kVDim, buf)) return e;
     CU_TRY(c, cudaMemcpy(c->layers[layer].w_uv, buf.data(), buf.size() * 2, cudaMemcpyHostToDevice));
@@ -876,6 +975,40 @@ int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const ui
         }
     }
     if (int e = upload_meta(c, seqs, rows, true, st)) return e;
+    // table offsets of the step's sequences inside the upload (the prefill path gathers rows through them)
+    c->step_tbl_off.resize(n_seq);
+    {
+        uint32_t o = 0;
+        for (uint32_t i = 0; i < n_seq; i++) { c->step_tbl_off[i] = o; o += uint32_t(c->pt->seq(seqs[i])->pages.size()); }
+    }
+    c->step_rows = uint32_t(rows.size());
+    c->chunks.clear();
+    c->has_plan_b = false;
+    bool any_chunk = false;
+    for (uint32_t i = 0; i < n_seq; i++) any_chunk = any_chunk || nn[i] >= kPrefillMin;
+    if (any_chunk && c->kernel != MLA_KERNEL_MMA) {
+        std::vector<RowSpec> rows_b;
+        std::vector<uint32_t> att_row;
+        uint32_t r = 0;
+        for (uint32_t i = 0; i < n_seq; i++) {
+            const auto* sq = c->pt->seq(seqs[i]);
+            const uint32_t cnt = std::max<uint32_t>(nn[i], 1);
+            if (nn[i] >= kPrefillMin) {
+                c->chunks.push_back({seqs[i], r, nn[i], sq->len, sq->base_pos});
+            } else {
+                for (uint32_t t = 0; t < cnt; t++) { rows_b.push_back(rows[r + t]); att_row.push_back(r + t); }
+            }
+            r += cnt;
+        }
+        const uint32_t plan_workers = c->plan_workers, plan_min = c->plan_min_pages, plan_max = c->plan_max_pages;
+        if (int e = upload_meta(c, seqs, rows_b, true, st, true, &att_row)) return e;
+        (void)plan_workers; (void)plan_min; (void)plan_max;
+        // the append of the second plan still writes every new row of the step, in the caller's order
+        c->meta_b.app_rows = c->meta.rows;
+        c->meta_b.app_pos = c->meta.row_pos;
+        c->meta_b.app_slot = c->meta.row_slot;
+        c->has_plan_b = true;
+    }
     c->step_seqs = std::move(seqs);
     c->step_nnew = std::move(nn);
     c->in_step = true;

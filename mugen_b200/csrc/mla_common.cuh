@@ -88,6 +88,13 @@ struct StepMeta {
     const uint32_t* row_seg_begin;  // [rows+1]  a row's segments are contiguous
     const uint32_t* cta_seg_begin;  // [ctas+1]  a persistent block's segments are contiguous
     uint32_t rows, segs, ctas;
+    // The step's new tokens, in the caller's row order (kv_a rows): what the append writes.  Usually the same rows as
+    // the query rows above; a step that routes long chunks to the prefill path keeps them here but not among the
+    // query rows, which then carry the index of their row in the caller's q / out tensors.
+    uint32_t app_rows;
+    const uint32_t* app_pos;        // [app_rows]  global position (RoPE)
+    const uint64_t* app_slot;       // [app_rows]  destination token slot
+    const uint32_t* att_row;        // [rows]  query row -> row of the caller's q / out (nullptr: the same index)
 };
 
 }  // namespace mla

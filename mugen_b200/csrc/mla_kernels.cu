@@ -77,16 +77,16 @@ void launch_append(int dtype, const void* kv_a, void* layer_pool, uint64_t pool_
                    const void* norm_w, const float* cos_sin, uint32_t cs_rows, float eps,
                    const StepMeta& m, uint32_t* status, cudaStream_t st)
 {
-    if (m.rows == 0) return;
+    if (m.app_rows == 0) return;
     if (dtype == 0)
-        append_kernel<__half><<<m.rows, 128, 0, st>>>(
+        append_kernel<__half><<<m.app_rows, 128, 0, st>>>(
             static_cast<const __half*>(kv_a), static_cast<__half*>(layer_pool), pool_slots,
-            static_cast<const __half*>(norm_w), cos_sin, cs_rows, eps, m.row_pos, m.row_slot, status);
+            static_cast<const __half*>(norm_w), cos_sin, cs_rows, eps, m.app_pos, m.app_slot, status);
     else
-        append_kernel<__nv_bfloat16><<<m.rows, 128, 0, st>>>(
+        append_kernel<__nv_bfloat16><<<m.app_rows, 128, 0, st>>>(
             static_cast<const __nv_bfloat16*>(kv_a), static_cast<__nv_bfloat16*>(layer_pool),
-            pool_slots, static_cast<const __nv_bfloat16*>(norm_w), cos_sin, cs_rows, eps, m.row_pos,
-            m.row_slot, status);
+            pool_slots, static_cast<const __nv_bfloat16*>(norm_w), cos_sin, cs_rows, eps, m.app_pos,
+            m.app_slot, status);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -235,7 +235,7 @@ template <typename T, int RT>
 __global__ void __launch_bounds__(256)
 merge_outproj_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin,
                      uint32_t n_parts, const T* __restrict__ w_uv, T* __restrict__ out,
-                     float* __restrict__ exported, uint32_t rows, uint32_t H)
+                     float* __restrict__ exported, uint32_t rows, uint32_t H, const uint32_t* __restrict__ att_row)
 {
     __shared__ __align__(16) float oc[RT][kRank];
     const uint32_t h = blockIdx.x, r0 = blockIdx.y * RT, tid = threadIdx.x;
@@ -303,7 +303,7 @@ merge_outproj_kernel(const float* __restrict__ recs, const uint32_t* __restrict_
             float v = 0.0f;
 #pragma unroll
             for (int rr = 0; rr < RT; rr++) v = (lane == rr) ? s[rr] : v;
-            out[(size_t(r0 + lane) * H + h) * kVDim + j] = Elem<T>::from_f32(v);
+            out[(size_t(att_row ? att_row[r0 + lane] : r0 + lane) * H + h) * kVDim + j] = Elem<T>::from_f32(v);
         }
     }
 }
@@ -324,7 +324,7 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 merge_outproj_mma_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin,
                          uint32_t n_parts, const T* __restrict__ w_uv, T* __restrict__ out, uint32_t rows,
-                         uint32_t H)
+                         uint32_t H, const uint32_t* __restrict__ att_row)
 {
     constexpr int PITCH = kMergePitch;
     extern __shared__ __align__(16) unsigned char merge_smem[];
@@ -435,9 +435,9 @@ merge_outproj_mma_kernel(const float* __restrict__ recs, const uint32_t* __restr
         }
         const int col = warp * 8 + t4 * 2;
         if (r0 + g < rows)
-            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g) * H + h) * kVDim + col) = Elem<T>::pack2(c[0], c[1]);
+            *reinterpret_cast<uint32_t*>(out + (size_t(att_row ? att_row[r0 + g] : r0 + g) * H + h) * kVDim + col) = Elem<T>::pack2(c[0], c[1]);
         if (r0 + g + 8 < rows)
-            *reinterpret_cast<uint32_t*>(out + (size_t(r0 + g + 8) * H + h) * kVDim + col) = Elem<T>::pack2(c[2], c[3]);
+            *reinterpret_cast<uint32_t*>(out + (size_t(att_row ? att_row[r0 + g + 8] : r0 + g + 8) * H + h) * kVDim + col) = Elem<T>::pack2(c[2], c[3]);
         __syncthreads();                                 // a_hi / a_lo / row_* are rewritten by the next tile
     }
 }
@@ -453,7 +453,7 @@ int merge_mma_configure()
 
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
-                  cudaStream_t st)
+                  cudaStream_t st, const uint32_t* att_row)
 {
     if (rows == 0) return;
     if (!exported) {
@@ -461,11 +461,11 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
         dim3 grid16(H, (row_tiles + kMergeTilesPerBlock - 1) / kMergeTilesPerBlock);
         if (dtype == 0)
             merge_outproj_mma_kernel<__half><<<grid16, 512, kMergeSmem, st>>>(
-                recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv), static_cast<__half*>(out), rows, H);
+                recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv), static_cast<__half*>(out), rows, H, att_row);
         else
             merge_outproj_mma_kernel<__nv_bfloat16><<<grid16, 512, kMergeSmem, st>>>(
                 recs, row_seg_begin, n_parts, static_cast<const __nv_bfloat16*>(w_uv),
-                static_cast<__nv_bfloat16*>(out), rows, H);
+                static_cast<__nv_bfloat16*>(out), rows, H, att_row);
         return;
     }
     constexpr int RT = 8;
@@ -473,11 +473,11 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
     if (dtype == 0)
         merge_outproj_kernel<__half, RT><<<grid, 256, 0, st>>>(
             recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv),
-            static_cast<__half*>(out), exported, rows, H);
+            static_cast<__half*>(out), exported, rows, H, att_row);
     else
         merge_outproj_kernel<__nv_bfloat16, RT><<<grid, 256, 0, st>>>(
             recs, row_seg_begin, n_parts, static_cast<const __nv_bfloat16*>(w_uv),
-            static_cast<__nv_bfloat16*>(out), exported, rows, H);
+            static_cast<__nv_bfloat16*>(out), exported, rows, H, att_row);
 }
 
 }  // namespace mla

@@ -49,7 +49,7 @@ int decode_tc5_pair128_configure();
 
 void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts,
                   const void* w_uv, void* out, float* exported, uint32_t rows, uint32_t H,
-                  cudaStream_t st);
+                  cudaStream_t st, const uint32_t* att_row = nullptr);
 int merge_mma_configure();
 
 // Absorb on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the layer's W_UK^T,
@@ -65,7 +65,7 @@ int absorb_tc5_configure();
 // The same merge + projection on tcgen05 (one block per head and 64 rows); w_map: host CUtensorMap over the
 // layer's W_UV, [H*128 outputs][512 dims], box 64 dims x 128 outputs, 128-byte swizzle.
 int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, const void* w_map,
-                     void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st);
+                     void* out, uint32_t rows, uint32_t H, const uint32_t* att_row, uint32_t* status, cudaStream_t st);
 int merge_tc5_configure();
 
 // Dense projection C = A . W^T on tcgen05 (mla_gemm_tc5.cu).  A [M][K] pitch lda, W [N][K] pitch ldw (the reference's
@@ -79,6 +79,16 @@ int launch_gemm_finalize(int dtype, const float* partial, uint32_t splits, uint3
 int launch_rmsnorm_rows(int dtype, const void* x, const void* w, void* y, uint32_t rows, uint32_t N, float eps, cudaStream_t st);
 uint32_t gemm_tc5_splits(uint32_t M, uint32_t N, uint32_t K, uint32_t sm_count);   // K slices that fill the SMs once
 int gemm_tc5_configure();
+
+// Chunked prefill (mla_prefill_tc5.cu): gather of a sequence's latent rows into a contiguous buffer, rotation of a
+// chunk's query rows, and causal flash attention of one chunk over expanded keys / values (see the file's header).
+int launch_gather_rows(const void* layer_pool, uint64_t pool_slots, const uint32_t* table, uint32_t n, void* dst, uint32_t* status,
+                       cudaStream_t st);
+int launch_rotate_q_rows(int dtype, const void* q_in, void* q_out, uint32_t rows, uint32_t H, uint32_t pos0, const float* cos_sin,
+                         uint32_t cs_rows, uint32_t* status, cudaStream_t st);
+int launch_prefill_tc5(int dtype, const void* q, uint32_t q_rows_total, uint32_t q_row0, uint32_t n_new, uint32_t start,
+                       const void* kx, const void* vx, const void* latent, void* out, uint32_t H, uint32_t* status, cudaStream_t st);
+int prefill_tc5_configure();
 
 // One block that waits `limit_cycles` on a barrier nothing completes, raises ST_WAIT_TIMEOUT in *status, frees its
 // tensor memory and returns; report[0] = 0 when the wait gave up, report[1] = cycles waited.

@@ -47,7 +47,7 @@ template <typename T, bool kSmall>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float* __restrict__ recs,
                          const uint32_t* __restrict__ row_seg_begin, uint32_t n_parts, T* __restrict__ out,
-                         uint32_t rows, uint32_t H, uint32_t* __restrict__ status)
+                         uint32_t rows, uint32_t H, const uint32_t* __restrict__ att_row, uint32_t* __restrict__ status)
 {
     extern __shared__ unsigned char merge_tc5_smem[];
     const uint32_t raw = smem_u32(merge_tc5_smem);
@@ -278,7 +278,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
                 tc_ld32(tmem + ((warp * 32u) << 16) + c * 32, o);
                 tc_wait_ld();
                 if (lane < 16 && row < rows) {
-                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t(row) * H + h) * kVDim + c * 32);
+                    uint4* dst = reinterpret_cast<uint4*>(out + (size_t(att_row ? att_row[row] : row) * H + h) * kVDim + c * 32);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         uint32_t pk[4];
@@ -322,13 +322,13 @@ int merge_tc5_configure()
 
 // w_map: host CUtensorMap over this layer's W_UV ([H*128 outputs][512 dims], box 64 dims x 128 outputs, 128-byte swizzle)
 int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin, uint32_t n_parts, const void* w_map,
-                     void* out, uint32_t rows, uint32_t H, uint32_t* status, cudaStream_t st)
+                     void* out, uint32_t rows, uint32_t H, const uint32_t* att_row, uint32_t* status, cudaStream_t st)
 {
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
     dim3 grid(H, (rows + MT - 1) / MT);
     auto go = [&](auto kernel, auto* o) {
-        return int(launch_pdl(kernel, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin, n_parts, o, rows, H, status));
+        return int(launch_pdl(kernel, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin, n_parts, o, rows, H, att_row, status));
     };
     const bool small = rows <= 16;
     if (dtype == 0)

@@ -416,6 +416,57 @@ def test_prefill_chunk_is_causal(torch, oracle, kernel):
     ctx.close()
 
 
+@pytest.mark.parametrize("H,dt,spec,q_rope", [
+    (16, synth.DT_F16, [(50, 70), (33, 1)], False),                  # one chunk next to a decode row
+    (5, synth.DT_BF16, [(0, 64), (0, 129)], False),                  # chunks from empty sequences, odd head count
+    (128, synth.DT_BF16, [(100, 1), (200, 300), (64, 2), (77, 128)], False),   # chunks, a decode row and a 2-token verify row
+    (32, synth.DT_F16, [(130, 200), (40, 1)], True),                 # queries arrive before their RoPE
+])
+def test_prefill_chunks_take_the_expanded_path(torch, oracle, H, dt, spec, q_rope):
+    """Sequences that take >= 64 new tokens in a step are routed, by mla_step_layers, through the prefill kernels
+    (latent rows expanded into per-head keys / values, causal flash attention), the other rows of the same step through
+    the decode kernels.  Chunk token t must see exactly [0, start + t + 1) (transformer.cpp:1325-1337): sampled tokens
+    of every chunk, and every other row, against the CPU attention; appended rows bit-equal to the checker's."""
+    from mugen_b200.mla import MlaContext
+    starts, n_new = [a for a, _ in spec], [b for _, b in spec]
+    R = sum(n_new)
+    case = synth.make_layer_case(4000 + H, H, [a + b for a, b in spec], dt)
+    ctx = MlaContext(n_layers=1, n_heads=H, dtype=dt, n_pages=sum((a + b) // 64 + 2 for a, b in spec), max_seqs=len(spec),
+                     max_seq_len=max(a + b for a, b in spec) + 64, max_rows=R, kernel=capi.KERNEL_AUTO, **YARN)
+    ctx.shuffle_free_pages(3)
+    ctx.set_layer_weights(0, case.w_uk, case.w_uv, case.w_type, case.norm_w)
+    seqs = fill(torch, ctx, case, upto=starts)
+    rng = np.random.default_rng(77)
+    kv = synth.to_bits(rng.standard_normal((R, 576), np.float32), dt)
+    q_raw = synth.to_bits(rng.standard_normal((R, H, 192), np.float32) * np.float32(0.9), dt)
+    pos, row0 = [], []
+    for a, b in spec:
+        row0.append(len(pos))
+        pos += [a + t for t in range(b)]
+    q_rot = q_raw
+    if q_rope:
+        q_rot = q_raw.copy()
+        for r in range(R):
+            q_rot[r] = oracle.q_rope(q_raw[r], pos[r], 40.0, 4096, 10000.0, dt)
+        ctx.set_q_rope(True)
+    out = torch.zeros((R, H, 128), dtype=torch.int16, device="cuda")
+    ctx.step_begin(seqs, n_new)
+    ctx.step_layers(0, 1, _dev(torch, kv)[None], _dev(torch, q_raw)[None], out[None])
+    ctx.step_end()
+    assert ctx.status() == 0
+    got = _host(out)
+    rows = oracle.append_rows(kv, pos, case.norm_w, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, dt)
+    for i, (a, b) in enumerate(spec):
+        assert ctx.seq_len(seqs[i]) == a + b
+        assert np.array_equal(ctx.read_rows(0, seqs[i], a, b), rows[row0[i]:row0[i] + b]), f"appended rows of sequence {i}"
+        cache = np.concatenate([case.caches[i][:a], rows[row0[i]:row0[i] + b]])
+        ts = sorted(set(t for t in (0, 1, 62, 63, 64, 65, 127, 128, b // 2, b - 2, b - 1) if 0 <= t < b))
+        for t in ts:
+            want = oracle.attention(q_rot[row0[i] + t], cache, a + t + 1, case.w_uk, case.w_uv, case.w_type, H, dt)
+            check_close(got[row0[i] + t], want, dt, f"sequence {i} (start {a}, {b} new), token {t}")
+    ctx.close()
+
+
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_kv_range_shards_merge(torch, oracle, kernel):
     """One sequence cut into 3 KV ranges held by 3 contexts (stand-ins for 3 GPUs): each emits
