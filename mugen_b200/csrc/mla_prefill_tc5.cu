@@ -12,14 +12,16 @@
 //
 // One block per (tile of 128 query tokens, head):
 //   TMA      Q tile [128][192] once; per 64-token step K [64][192] (two boxes of expanded nope dims + one box of rope dims
-//            straight from the gathered latent rows) and V [64][128], three stages
+//            straight from the gathered latent rows) in a ring of three, V [64][128] in a ring of four: a K buffer is free as
+//            soon as the score MMAs that read it complete, a V buffer one softmax later
 //   QK       S[128 queries x 64 keys] = Q . K^T          12 x tcgen05.mma M128 N64 K16, scores double-buffered in TMEM
-//   softmax  thread = query row: causal mask, log2-domain online softmax with lazy rescaling (threshold 2^8), P to
-//            shared memory in the storage type
+//   softmax  two threads per query row, 32 keys each (the two halves of a row exchange their maxima through shared
+//            memory): causal mask, log2-domain online softmax with lazy rescaling (threshold 2^8), P to shared memory in
+//            the storage type.  Two softmax warps per scheduler hide each other's dependent-issue latency.
 //   PV       O^T[128 value dims x 128 queries] += V^T . P^T   4 x tcgen05.mma M128 N128 K16 with the V tile read MN-major
 //            (the staged [64 keys][64 dims] sub-tiles serve as they are, no transpose), B = P (K-major)
 //   epilogue O^T / l -> out[query][head][128], rounded once to the storage type
-// Warps: 0 TMA producer, 1 MMA issuer, 2-5 softmax / correction / epilogue.  All waits are bounded.
+// Warps: 0 TMA producer, 1 MMA issuer, 2-9 softmax / correction / epilogue.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
@@ -37,18 +39,23 @@ constexpr int QT = 128, KT = 64;
 constexpr int Q_SUB = QT * 128;                        // 16,384: [128 queries][64 dims]
 constexpr int K_SUB = KT * 128;                        // 8,192:  [64 keys][64 dims]
 constexpr int Q_BYTES = 3 * Q_SUB;                     // 49,152
-constexpr int STAGE_BYTES = 3 * K_SUB + 2 * K_SUB;     // K (192 dims) + V (128 dims) = 40,960
-constexpr int STAGES = 3;
+constexpr int K_STAGE = 3 * K_SUB, V_STAGE = 2 * K_SUB;        // K: 192 dims, V: 128 dims of 64 keys
+constexpr int K_STAGES = 3, V_STAGES = 4;
 constexpr int P_BYTES = QT * 128;                      // 16,384: [128 queries][64 keys]
-constexpr int OFF_Q = 0, OFF_KV = OFF_Q + Q_BYTES, OFF_P = OFF_KV + STAGES * STAGE_BYTES, OFF_MISC = OFF_P + P_BYTES;
-constexpr int M_ALPHA = 128, M_LINV = 128 + 1024, M_TMEM = 128 + 1536, M_ABORT = M_TMEM + 4, MISC_BYTES = 128 + 1536 + 64;   // alpha: [2][128] by step parity
+constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + K_STAGES * K_STAGE, OFF_P = OFF_V + V_STAGES * V_STAGE,
+              OFF_MISC = OFF_P + P_BYTES;
+// alpha: [2][128] by step parity; hmax / lsum: [2 halves][128 rows]
+constexpr int M_ALPHA = 256, M_HMAX = M_ALPHA + 1024, M_LSUM = M_HMAX + 1024, M_LINV = M_LSUM + 1024, M_TMEM = M_LINV + 512,
+              M_ABORT = M_TMEM + 4, MISC_BYTES = M_TMEM + 64;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;       // + slack for 1 KB alignment
-constexpr int NUM_THREADS = 32 * 6;
+constexpr int NUM_SOFTMAX = 256;
+constexpr int NUM_THREADS = 64 + NUM_SOFTMAX;
 constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_O = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;
-enum { B_QFULL = 0, B_KVFULL, B_KVEMPTY = B_KVFULL + STAGES, B_SFULL = B_KVEMPTY + STAGES, B_SEMPTY = B_SFULL + 2,
-       B_PFULL = B_SEMPTY + 2, B_PEMPTY, B_OFULL, B_COUNT };
-static_assert(B_COUNT * 8 <= 128, "barriers overflow their area");
+enum { B_QFULL = 0, B_KFULL, B_KEMPTY = B_KFULL + K_STAGES, B_VFULL = B_KEMPTY + K_STAGES, B_VEMPTY = B_VFULL + V_STAGES,
+       B_SFULL = B_VEMPTY + V_STAGES, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2, B_PEMPTY, B_OFULL, B_COUNT };
+static_assert(B_COUNT * 8 <= M_ALPHA && B_COUNT <= 32, "barriers overflow their area");
+static_assert(SMEM_BYTES <= 232448, "over the shared memory of one block");
 
 struct ChunkArgs {
     uint32_t q_row0;        // first query row of the chunk in the q / out tensors
@@ -67,9 +74,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t raw = smem_u32(prefill_smem);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm = prefill_smem + (base - raw);
-    const uint32_t sQ = base + OFF_Q, sKV = base + OFF_KV, sP = base + OFF_P, sBar = base + OFF_MISC;
+    const uint32_t sQ = base + OFF_Q, sK = base + OFF_K, sV = base + OFF_V, sP = base + OFF_P, sBar = base + OFF_MISC;
     auto bar = [&](int i) { return sBar + 8u * uint32_t(i); };
     float* alpha_s = reinterpret_cast<float*>(sm + OFF_MISC + M_ALPHA);
+    float* hmax_s = reinterpret_cast<float*>(sm + OFF_MISC + M_HMAX);
+    float* lsum_s = reinterpret_cast<float*>(sm + OFF_MISC + M_LSUM);
     float* linv_s = reinterpret_cast<float*>(sm + OFF_MISC + M_LINV);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_ABORT);
@@ -85,7 +94,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     grid_launch_dependents();
     if (warp == 0 && lane < B_COUNT) {
         const int i = int(lane);
-        const uint32_t count = (i >= B_SEMPTY && i < B_PFULL) || i == B_PFULL ? 128u : 1u;
+        const uint32_t count = (i >= B_SEMPTY && i < B_PFULL) || i == B_PFULL ? uint32_t(NUM_SOFTMAX) : 1u;
         mbar_init(bar(i), count);
     }
     if (warp == 0) mbar_init_fence();
@@ -105,16 +114,20 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tma_load_2d(sQ + c * Q_SUB, &map_q, bar(B_QFULL), int(h * kQDim + 64 * c), int(a.q_row0 + q0));
             bool ok = true;
             for (uint32_t t = 0; t < n_kv && ok; t++) {
-                const int s = int(t % STAGES);
-                ok = mbar_wait(bar(B_KVEMPTY + s), ((t / STAGES) & 1) ^ 1, abort_flag, status);
+                const int ks = int(t % K_STAGES), vs = int(t % V_STAGES);
+                ok = mbar_wait(bar(B_KEMPTY + ks), ((t / K_STAGES) & 1) ^ 1, abort_flag, status);
                 if (!ok) break;
-                const uint32_t dst = sKV + s * STAGE_BYTES;
-                mbar_expect_tx(bar(B_KVFULL + s), STAGE_BYTES);
-                tma_load_2d(dst, &map_k, bar(B_KVFULL + s), int(h * kNope), int(t * KT));
-                tma_load_2d(dst + K_SUB, &map_k, bar(B_KVFULL + s), int(h * kNope + 64), int(t * KT));
-                tma_load_2d(dst + 2 * K_SUB, &map_r, bar(B_KVFULL + s), kRank, int(t * KT));
-                tma_load_2d(dst + 3 * K_SUB, &map_v, bar(B_KVFULL + s), int(h * kVDim), int(t * KT));
-                tma_load_2d(dst + 4 * K_SUB, &map_v, bar(B_KVFULL + s), int(h * kVDim + 64), int(t * KT));
+                const uint32_t kd = sK + ks * K_STAGE;
+                mbar_expect_tx(bar(B_KFULL + ks), K_STAGE);
+                tma_load_2d(kd, &map_k, bar(B_KFULL + ks), int(h * kNope), int(t * KT));
+                tma_load_2d(kd + K_SUB, &map_k, bar(B_KFULL + ks), int(h * kNope + 64), int(t * KT));
+                tma_load_2d(kd + 2 * K_SUB, &map_r, bar(B_KFULL + ks), kRank, int(t * KT));
+                ok = mbar_wait(bar(B_VEMPTY + vs), ((t / V_STAGES) & 1) ^ 1, abort_flag, status);
+                if (!ok) break;
+                const uint32_t vd = sV + vs * V_STAGE;
+                mbar_expect_tx(bar(B_VFULL + vs), V_STAGE);
+                tma_load_2d(vd, &map_v, bar(B_VFULL + vs), int(h * kVDim), int(t * KT));
+                tma_load_2d(vd + K_SUB, &map_v, bar(B_VFULL + vs), int(h * kVDim + 64), int(t * KT));
             }
         }
     } else if (warp == 1) {
@@ -123,29 +136,30 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         constexpr uint32_t HI = desc_hi(1024);
         bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, status);
         auto issue_pv = [&](uint32_t t) {           // O^T += V(t)^T . P(t)^T
-            ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+            const int vs = int(t % V_STAGES);
+            ok = mbar_wait(bar(B_VFULL + vs), (t / V_STAGES) & 1, abort_flag, status) &&
+                 mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
             if (!ok) return;
             tc_fence_after();
             if (elect_one()) {
-                const uint32_t v0 = sKV + (t % STAGES) * STAGE_BYTES + 3 * K_SUB;
-                const uint32_t pa = desc_lo(v0, K_SUB), pb = desc_lo(sP);
+                const uint32_t pa = desc_lo(sV + vs * V_STAGE, K_SUB), pb = desc_lo(sP);
 #pragma unroll
                 for (int k = 0; k < KT / 16; k++)
                     tc_mma(tmem + COL_O, pa + ((k * 2048) >> 4), HI, pb + ((k * 32) >> 4), HI, IDESC_PV, (t == 0 && k == 0) ? 0u : 1u);
-                tc_commit(bar(B_KVEMPTY + int(t % STAGES)));
+                tc_commit(bar(B_VEMPTY + vs));
                 tc_commit(bar(B_PEMPTY));
                 if (t + 1 == n_kv) tc_commit(bar(B_OFULL));
             }
             __syncwarp();
         };
         for (uint32_t t = 0; t < n_kv && ok; t++) {
-            const int s = int(t % STAGES), b = int(t & 1);
-            ok = mbar_wait(bar(B_KVFULL + s), (t / STAGES) & 1, abort_flag, status) &&
+            const int ks = int(t % K_STAGES), b = int(t & 1);
+            ok = mbar_wait(bar(B_KFULL + ks), (t / K_STAGES) & 1, abort_flag, status) &&
                  mbar_wait(bar(B_SEMPTY + b), ((t >> 1) & 1) ^ 1, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
             if (elect_one()) {
-                const uint32_t qa = desc_lo(sQ), kb = desc_lo(sKV + s * STAGE_BYTES);
+                const uint32_t qa = desc_lo(sQ), kb = desc_lo(sK + ks * K_STAGE);
 #pragma unroll
                 for (int c = 0; c < 3; c++)
 #pragma unroll
@@ -153,87 +167,88 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         tc_mma(tmem + COL_S + b * KT, qa + ((c * Q_SUB + k * 32) >> 4), HI, kb + ((c * K_SUB + k * 32) >> 4), HI,
                                IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
                 tc_commit(bar(B_SFULL + b));
+                tc_commit(bar(B_KEMPTY + ks));
             }
             __syncwarp();
             if (t > 0) issue_pv(t - 1);
         }
         if (ok && n_kv > 0) issue_pv(n_kv - 1);
     } else {
-        // ===================== softmax / correction / epilogue: thread = query row (scores), = value dim (O^T) =====
-        const uint32_t q4 = warp % 4, r = q4 * 32 + lane;                // TMEM lane of this thread
+        // ===== softmax / correction / epilogue: two threads per query row (32 keys each); for O^T: thread = value dim =====
+        const uint32_t q4 = warp % 4, half = (warp - 2) / 4, r = q4 * 32 + lane;   // r: TMEM lane of this thread
         const uint32_t lane_base = (q4 * 32u) << 16;
         const uint32_t my_pos = a.start + q0 + r;                        // last key this query may see
-        float m_run = -INFINITY, l_run = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;                           // l_run: this half's share of the row sum
         bool fail = false;
         auto wait_w = [&](uint32_t b, uint32_t parity) {
             if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
             fail = __any_sync(0xffffffffu, fail);
         };
-        auto group_or = [&](bool pred) -> bool {              // barrier over the 128 softmax threads + OR
+        auto group_or = [&](bool pred) -> bool {              // barrier over the softmax threads + OR
             uint32_t rr;
             asm volatile(
                 "{\n.reg .pred pi, po;\n"
                 "setp.ne.b32 pi, %1, 0;\n"
-                "barrier.cta.red.or.pred po, 1, 128, pi;\n"
+                "barrier.cta.red.or.pred po, 1, %2, pi;\n"
                 "selp.u32 %0, 1, 0, po;\n}\n"
-                : "=r"(rr) : "r"(uint32_t(pred)) : "memory");
+                : "=r"(rr) : "r"(uint32_t(pred)), "n"(NUM_SOFTMAX) : "memory");
             return rr != 0;
         };
+        auto group_sync = [&]() { asm volatile("barrier.cta.sync 2, %0;\n" :: "n"(NUM_SOFTMAX) : "memory"); };
         bool stop = false;
         for (uint32_t t = 0; t < n_kv; t++) {
             const uint32_t b = t & 1;
             wait_w(bar(B_SFULL + b), (t >> 1) & 1);
-            uint32_t sv[64];
+            uint32_t sv[32];
             if (!fail) {
                 tc_fence_after();
-                uint32_t lo[32], hi[32];
-                tc_ld32(tmem + lane_base + COL_S + b * KT, lo);
-                tc_ld32(tmem + lane_base + COL_S + b * KT + 32, hi);
+                tc_ld32(tmem + lane_base + COL_S + b * KT + half * 32, sv);
                 tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i++) { sv[i] = lo[i]; sv[32 + i] = hi[i]; }
                 tc_fence_before();
                 mbar_arrive(bar(B_SEMPTY + b));
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; i++) sv[i] = 0u;
+                for (int i = 0; i < 32; i++) sv[i] = 0u;
             }
-            const uint32_t k0 = t * KT;
-            if (k0 + KT > my_pos + 1 || k0 + KT > total) {               // causal / end mask (only near the diagonal)
+            const uint32_t k0 = t * KT + half * 32;
+            if (k0 + 32 > my_pos + 1 || k0 + 32 > total) {               // causal / end mask (only near the diagonal)
 #pragma unroll
-                for (int i = 0; i < 64; i++)
+                for (int i = 0; i < 32; i++)
                     if (k0 + uint32_t(i) > my_pos || k0 + uint32_t(i) >= total) sv[i] = __float_as_uint(-INFINITY);
             }
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 64; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
-            mx *= scale_log2;
+            for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            hmax_s[half * QT + r] = mx;
+            group_sync();                                                // the next write of hmax_s comes after group_or below
+            mx = fmaxf(mx, hmax_s[(half ^ 1u) * QT + r]) * scale_log2;   // both halves of a row now hold the same maximum
             float alpha = 1.0f;
             bool need = false;
             if (m_run == -INFINITY) { m_run = mx; }                     // nothing accumulated for this row yet
             else if (mx > m_run + RESCALE_THRESHOLD) { alpha = fast_ex2(m_run - mx); m_run = mx; need = true; }
             float* alpha_t = alpha_s + (t & 1) * QT;     // by step parity: a fast thread may be one step ahead of a slow one
-            alpha_t[r] = alpha;
-            float sum = 0.0f;
-            uint32_t pk[32];
+            if (half == 0) alpha_t[r] = alpha;
+            float sum2[2] = {0.0f, 0.0f};
+            uint32_t pk[16];
             const float mref = m_run == -INFINITY ? 0.0f : m_run;         // a row whose keys so far are all masked: p = 0
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
+            for (int i = 0; i < 32; i += 2) {
                 const float p0 = fast_ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -mref));
                 const float p1 = fast_ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -mref));
-                sum += p0 + p1;
+                sum2[(i >> 1) & 1] += p0 + p1;
                 pk[i / 2] = Elem<T>::pack2(p0, p1);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + (sum2[0] + sum2[1]);
             const bool any_need = group_or(need || fail);
             if (any_need && group_or(fail)) { stop = true; break; }
             wait_w(bar(B_PEMPTY), (t - 1) & 1);          // PV of the previous step complete: O^T stable, P free
             if (fail) continue;
             tc_fence_after();
             if (any_need && t > 0) {
-                // O^T[value dim = this thread's lane][query column] *= alpha[query]
+                // O^T[value dim = this thread's lane][query column] *= alpha[query]; each half takes two of the four chunks
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (uint32_t c = 2 * half; c < 2 * half + 2; c++) {
                     uint32_t o[32];
                     tc_ld32(tmem + lane_base + COL_O + c * 32, o);
                     tc_wait_ld();
@@ -243,11 +258,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 tc_wait_st();
             }
-            {   // row r of the K-major swizzled P tile [128 queries][64 keys]: 8 chunks of 16 bytes
+            {   // row r of the K-major swizzled P tile [128 queries][64 keys]: this half's 4 of the 8 chunks of 16 bytes
                 unsigned char* prow = sm + OFF_P + r * 128;
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++)
-                    *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                for (int j = 0; j < 4; j++)
+                    *reinterpret_cast<uint4*>(prow + (((half * 4 + j) ^ (r & 7)) << 4)) =
+                        make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
@@ -255,12 +271,18 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (!stop) {
             wait_w(bar(B_OFULL), 0);
-            linv_s[r] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            if (!group_or(fail)) {
+            lsum_s[half * QT + r] = l_run;
+            const bool bad = group_or(fail);
+            if (half == 0) {
+                const float l = lsum_s[r] + lsum_s[QT + r];
+                linv_s[r] = l > 0.0f ? 1.0f / l : 0.0f;
+            }
+            group_sync();
+            if (!bad) {
                 tc_fence_after();
                 // this thread holds value dim r of every query column: out[query][h][r] = O^T[r][query] / l[query]
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (uint32_t c = 2 * half; c < 2 * half + 2; c++) {
                     uint32_t o[32];
                     tc_ld32(tmem + lane_base + COL_O + c * 32, o);
                     tc_wait_ld();
