@@ -10,18 +10,26 @@
 // over 192-dim keys and 128-dim values: 2 x (192 + 128) flops per (query, key, head) pair instead of the absorbed
 // form's 2 x (576 + 512), and each staged key/value tile serves 128 query tokens instead of one.
 //
-// One block per (tile of 128 query tokens, head):
-//   TMA      Q tile [128][192] once; per 64-token step K [64][192] (two boxes of expanded nope dims + one box of rope dims
-//            straight from the gathered latent rows) in a ring of three, V [64][128] in a ring of four: a K buffer is free as
-//            soon as the score MMAs that read it complete, a V buffer one softmax later
-//   QK       S[128 queries x 64 keys] = Q . K^T          12 x tcgen05.mma M128 N64 K16, scores double-buffered in TMEM
-//   softmax  two threads per query row, 32 keys each (the two halves of a row exchange their maxima through shared
-//            memory): causal mask, log2-domain online softmax with lazy rescaling (threshold 2^8), P to shared memory in
-//            the storage type.  Two softmax warps per scheduler hide each other's dependent-issue latency.
-//   PV       O^T[128 value dims x 128 queries] += V^T . P^T   4 x tcgen05.mma M128 N128 K16 with the V tile read MN-major
-//            (the staged [64 keys][64 dims] sub-tiles serve as they are, no transpose), B = P (K-major)
-//   epilogue O^T / l -> out[query][head][128], rounded once to the storage type
-// Warps: 0 TMA producer, 1 MMA issuer, 2-9 softmax / correction / epilogue.  All waits are bounded.
+// One block per (tile of 128 query tokens, head); the whole tile state lives in tensor memory:
+//   Q        [128 queries][192 dims] written once into tensor memory by the softmax threads (row = lane, two dims per
+//            column) and used as the A operand of every score MMA: no shared-memory reads for it
+//   TMA      per 64-token step K [64][192] (two boxes of expanded nope dims + one box of rope dims straight from the
+//            gathered latent rows) and V [64][128], rings of four each; a K buffer is free as soon as the score MMAs that
+//            read it complete, a V buffer one softmax later
+//   QK       S[128 queries x 64 keys] = Q . K^T          12 x tcgen05.mma M128 N64 K16 (A in tensor memory), three score
+//            tiles in flight
+//   softmax  four threads per query row, 16 keys each (the parts of a row exchange their maxima through shared memory;
+//            four softmax warps per scheduler hide each other's dependent-issue latency): causal mask, log2-domain online
+//            softmax with lazy rescaling (threshold 2^8); P in the storage type goes back into the tensor-memory columns
+//            its scores came from
+//   PV       O[128 queries x 128 value dims] += P . V    4 x tcgen05.mma M128 N128 K16, A = P in tensor memory, B = the
+//            staged V tile read MN-major (no transpose)
+//   rescale  a row whose maximum moved rescales its own O row (its own lane) after the previous PV completes; no
+//            block-wide agreement is needed
+//   epilogue O / l -> out[query][head][128], rounded once to the storage type
+// The tensor core reads only K and V from shared memory (6 KB per MMA step would be 2 + 4 KB with Q and P there too).
+// Warps: 0 TMA producer, 1 score-MMA issuer, 2 PV-MMA issuer (two issuers keep the tensor pipe fed while one of them
+// waits), 3.. softmax / correction / epilogue.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
@@ -36,25 +44,30 @@ namespace {
 using namespace tc5;
 
 constexpr int QT = 128, KT = 64;
-constexpr int Q_SUB = QT * 128;                        // 16,384: [128 queries][64 dims]
 constexpr int K_SUB = KT * 128;                        // 8,192:  [64 keys][64 dims]
-constexpr int Q_BYTES = 3 * Q_SUB;                     // 49,152
 constexpr int K_STAGE = 3 * K_SUB, V_STAGE = 2 * K_SUB;        // K: 192 dims, V: 128 dims of 64 keys
-constexpr int K_STAGES = 3, V_STAGES = 4;
-constexpr int P_BYTES = QT * 128;                      // 16,384: [128 queries][64 keys]
-constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + K_STAGES * K_STAGE, OFF_P = OFF_V + V_STAGES * V_STAGE,
-              OFF_MISC = OFF_P + P_BYTES;
-// alpha: [2][128] by step parity; hmax / lsum: [2 halves][128 rows]
-constexpr int M_ALPHA = 256, M_HMAX = M_ALPHA + 1024, M_LSUM = M_HMAX + 1024, M_LINV = M_LSUM + 1024, M_TMEM = M_LINV + 512,
-              M_ABORT = M_TMEM + 4, MISC_BYTES = M_TMEM + 64;
+constexpr int K_STAGES = 4, V_STAGES = 4;
+constexpr int OFF_K = 0, OFF_V = OFF_K + K_STAGES * K_STAGE, OFF_MISC = OFF_V + V_STAGES * V_STAGE;
+#ifndef MLA_PREFILL_NS
+#define MLA_PREFILL_NS 2
+#endif
+constexpr int NS = MLA_PREFILL_NS;                     // softmax threads per query row (2 or 4)
+constexpr int KP = KT / NS, QP = kQDim / NS, VP = kVDim / NS;   // keys, query dims, value dims per thread of a row
+// hmax: [2 step parities][NS parts][128 rows]; lsum: [NS parts][128 rows]
+constexpr int M_HMAX = 256, M_LSUM = M_HMAX + 2 * NS * QT * 4, M_TMEM = M_LSUM + NS * QT * 4, M_ABORT = M_TMEM + 4, MISC_BYTES = M_TMEM + 64;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;       // + slack for 1 KB alignment
-constexpr int NUM_SOFTMAX = 256;
-constexpr int NUM_THREADS = 64 + NUM_SOFTMAX;
-constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_O = 128;
+constexpr int NUM_SOFTMAX = NS * QT;
+constexpr int FIRST_SOFTMAX_WARP = 3;
+constexpr int NUM_THREADS = 32 * FIRST_SOFTMAX_WARP + NUM_SOFTMAX;
+// tensor memory columns: Q as 16-bit pairs (96), two score tiles (P of a step overwrites the head of each part of its
+// scores), O
+constexpr int S_BUFS = 3;                              // score tiles in flight: QK of step t + 1 never waits for softmax t
+constexpr uint32_t TMEM_COLS = 512, COL_Q = 0, COL_S = 128, COL_O = COL_S + S_BUFS * KT;
+static_assert(COL_O + kVDim <= TMEM_COLS, "tensor memory columns");
 constexpr float RESCALE_THRESHOLD = 8.0f;
 enum { B_QFULL = 0, B_KFULL, B_KEMPTY = B_KFULL + K_STAGES, B_VFULL = B_KEMPTY + K_STAGES, B_VEMPTY = B_VFULL + V_STAGES,
-       B_SFULL = B_VEMPTY + V_STAGES, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2, B_PEMPTY, B_OFULL, B_COUNT };
-static_assert(B_COUNT * 8 <= M_ALPHA && B_COUNT <= 32, "barriers overflow their area");
+       B_SFULL = B_VEMPTY + V_STAGES, B_PFULL = B_SFULL + S_BUFS, B_PVDONE, B_OFULL = B_PVDONE + S_BUFS, B_COUNT };
+static_assert(B_COUNT * 8 <= M_HMAX && B_COUNT <= 32, "barriers overflow their area");
 static_assert(SMEM_BYTES <= 232448, "over the shared memory of one block");
 
 struct ChunkArgs {
@@ -66,20 +79,18 @@ struct ChunkArgs {
 
 template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_r, ChunkArgs a,
-                   T* __restrict__ out, float scale_log2, uint32_t* __restrict__ status)
+prefill_tc5_kernel(const T* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const __grid_constant__ CUtensorMap map_r, ChunkArgs a, T* __restrict__ out, float scale_log2,
+                   uint32_t* __restrict__ status)
 {
     extern __shared__ unsigned char prefill_smem[];
     const uint32_t raw = smem_u32(prefill_smem);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm = prefill_smem + (base - raw);
-    const uint32_t sQ = base + OFF_Q, sK = base + OFF_K, sV = base + OFF_V, sP = base + OFF_P, sBar = base + OFF_MISC;
+    const uint32_t sK = base + OFF_K, sV = base + OFF_V, sBar = base + OFF_MISC;
     auto bar = [&](int i) { return sBar + 8u * uint32_t(i); };
-    float* alpha_s = reinterpret_cast<float*>(sm + OFF_MISC + M_ALPHA);
     float* hmax_s = reinterpret_cast<float*>(sm + OFF_MISC + M_HMAX);
     float* lsum_s = reinterpret_cast<float*>(sm + OFF_MISC + M_LSUM);
-    float* linv_s = reinterpret_cast<float*>(sm + OFF_MISC + M_LINV);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_ABORT);
 
@@ -94,8 +105,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     grid_launch_dependents();
     if (warp == 0 && lane < B_COUNT) {
         const int i = int(lane);
-        const uint32_t count = (i >= B_SEMPTY && i < B_PFULL) || i == B_PFULL ? uint32_t(NUM_SOFTMAX) : 1u;
-        mbar_init(bar(i), count);
+        mbar_init(bar(i), i == B_QFULL || i == B_PFULL ? uint32_t(NUM_SOFTMAX) : 1u);
     }
     if (warp == 0) mbar_init_fence();
     if (tid == 0) *abort_flag = 0;
@@ -108,10 +118,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(bar(B_QFULL), Q_BYTES);
-#pragma unroll
-            for (int c = 0; c < 3; c++)
-                tma_load_2d(sQ + c * Q_SUB, &map_q, bar(B_QFULL), int(h * kQDim + 64 * c), int(a.q_row0 + q0));
             bool ok = true;
             for (uint32_t t = 0; t < n_kv && ok; t++) {
                 const int ks = int(t % K_STAGES), vs = int(t % V_STAGES);
@@ -131,54 +137,78 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else if (warp == 1) {
+        // ---- score MMAs.  The score buffer of step t held P(t - S_BUFS): wait for the PV MMAs that read it.
         constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, QT, KT, 0, 0);
-        constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, kVDim, QT, 1, 0);
         constexpr uint32_t HI = desc_hi(1024);
         bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, status);
-        auto issue_pv = [&](uint32_t t) {           // O^T += V(t)^T . P(t)^T
-            const int vs = int(t % V_STAGES);
-            ok = mbar_wait(bar(B_VFULL + vs), (t / V_STAGES) & 1, abort_flag, status) &&
-                 mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
-            if (!ok) return;
-            tc_fence_after();
-            if (elect_one()) {
-                const uint32_t pa = desc_lo(sV + vs * V_STAGE, K_SUB), pb = desc_lo(sP);
-#pragma unroll
-                for (int k = 0; k < KT / 16; k++)
-                    tc_mma(tmem + COL_O, pa + ((k * 2048) >> 4), HI, pb + ((k * 32) >> 4), HI, IDESC_PV, (t == 0 && k == 0) ? 0u : 1u);
-                tc_commit(bar(B_VEMPTY + vs));
-                tc_commit(bar(B_PEMPTY));
-                if (t + 1 == n_kv) tc_commit(bar(B_OFULL));
-            }
-            __syncwarp();
-        };
         for (uint32_t t = 0; t < n_kv && ok; t++) {
-            const int ks = int(t % K_STAGES), b = int(t & 1);
+            const int ks = int(t % K_STAGES), b = int(t % S_BUFS);
             ok = mbar_wait(bar(B_KFULL + ks), (t / K_STAGES) & 1, abort_flag, status) &&
-                 mbar_wait(bar(B_SEMPTY + b), ((t >> 1) & 1) ^ 1, abort_flag, status);
+                 (t < S_BUFS || mbar_wait(bar(B_PVDONE + b), (t / S_BUFS - 1) & 1, abort_flag, status));
             if (!ok) break;
             tc_fence_after();
             if (elect_one()) {
-                const uint32_t qa = desc_lo(sQ), kb = desc_lo(sK + ks * K_STAGE);
+                const uint32_t kb = desc_lo(sK + ks * K_STAGE);
 #pragma unroll
                 for (int c = 0; c < 3; c++)
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        tc_mma(tmem + COL_S + b * KT, qa + ((c * Q_SUB + k * 32) >> 4), HI, kb + ((c * K_SUB + k * 32) >> 4), HI,
-                               IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
+                        tc_mma_ts(tmem + COL_S + b * KT, tmem + COL_Q + (c * 4 + k) * 8, kb + ((c * K_SUB + k * 32) >> 4), HI,
+                                  IDESC_QK, (c == 0 && k == 0) ? 0u : 1u);
                 tc_commit(bar(B_SFULL + b));
                 tc_commit(bar(B_KEMPTY + ks));
             }
             __syncwarp();
-            if (t > 0) issue_pv(t - 1);
         }
-        if (ok && n_kv > 0) issue_pv(n_kv - 1);
+    } else if (warp == 2) {
+        // ---- O += P(t) . V(t); P(t) sits where the scores of step t were
+        constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, QT, kVDim, 0, 1);
+        constexpr uint32_t HI = desc_hi(1024);
+        bool ok = true;
+        for (uint32_t t = 0; t < n_kv && ok; t++) {
+            const int vs = int(t % V_STAGES);
+            ok = mbar_wait(bar(B_VFULL + vs), (t / V_STAGES) & 1, abort_flag, status) &&
+                 mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one()) {
+                const uint32_t vb = desc_lo(sV + vs * V_STAGE, K_SUB), pa = tmem + COL_S + (t % S_BUFS) * KT;
+#pragma unroll
+                for (int k = 0; k < KT / 16; k++)    // keys 16k..: 8 columns at the head of the score columns of their part
+                    tc_mma_ts(tmem + COL_O, pa + (16 * k / KP) * KP + (16 * k % KP) / 2, vb + ((k * 2048) >> 4), HI, IDESC_PV,
+                              (t == 0 && k == 0) ? 0u : 1u);
+                tc_commit(bar(B_VEMPTY + vs));
+                tc_commit(bar(B_PVDONE + (t % S_BUFS)));
+                if (t + 1 == n_kv) tc_commit(bar(B_OFULL));
+            }
+            __syncwarp();
+        }
     } else {
-        // ===== softmax / correction / epilogue: two threads per query row (32 keys each); for O^T: thread = value dim =====
-        const uint32_t q4 = warp % 4, half = (warp - 2) / 4, r = q4 * 32 + lane;   // r: TMEM lane of this thread
+        // ===== softmax / correction / epilogue: NS threads per query row; the row is this thread's tensor-memory lane =====
+        static_assert(NS == 1 || NS == 2 || NS == 4, "the part sizes below");
+        const uint32_t q4 = warp % 4, part = (warp - FIRST_SOFTMAX_WARP) / 4, r = q4 * 32 + lane;
         const uint32_t lane_base = (q4 * 32u) << 16;
-        const uint32_t my_pos = a.start + q0 + r;                        // last key this query may see
-        float m_run = -INFINITY, l_run = 0.0f;                           // l_run: this half's share of the row sum
+        const uint32_t qi = q0 + r;                                      // query token within the chunk
+        const bool live = qi < a.n_new;
+        const uint32_t my_pos = a.start + qi;                            // last key this query may see
+        {   // this thread's part of the query row: QP dims = QP / 2 columns, in three stores
+            constexpr int W = QP / 6;
+            const uint4* src = reinterpret_cast<const uint4*>(q + (size_t(a.q_row0 + qi) * a.H + h) * kQDim + part * QP);
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                uint32_t w[W];
+#pragma unroll
+                for (int j = 0; j < W / 4; j++) {
+                    const uint4 v = live ? __ldg(src + c * (W / 4) + j) : make_uint4(0u, 0u, 0u, 0u);
+                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                }
+                tc_stn(tmem + lane_base + COL_Q + part * (QP / 2) + c * W, w);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(B_QFULL));
+        }
+        float m_run = -INFINITY, l_run = 0.0f;                           // l_run: this part's share of the row sum
         bool fail = false;
         auto wait_w = [&](uint32_t b, uint32_t parity) {
             if (!fail) fail = !mbar_wait(b, parity, abort_flag, status);
@@ -195,104 +225,95 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             return rr != 0;
         };
         auto group_sync = [&]() { asm volatile("barrier.cta.sync 2, %0;\n" :: "n"(NUM_SOFTMAX) : "memory"); };
-        bool stop = false;
         for (uint32_t t = 0; t < n_kv; t++) {
-            const uint32_t b = t & 1;
-            wait_w(bar(B_SFULL + b), (t >> 1) & 1);
-            uint32_t sv[32];
+            const uint32_t b = t % S_BUFS;
+            const uint32_t s_addr = tmem + lane_base + COL_S + b * KT + part * KP;
+            wait_w(bar(B_SFULL + b), (t / S_BUFS) & 1);
+            uint32_t sv[KP];
             if (!fail) {
                 tc_fence_after();
-                tc_ld32(tmem + lane_base + COL_S + b * KT + half * 32, sv);
+                tc_ldn(s_addr, sv);
                 tc_wait_ld();
-                tc_fence_before();
-                mbar_arrive(bar(B_SEMPTY + b));
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; i++) sv[i] = 0u;
+                for (int i = 0; i < KP; i++) sv[i] = 0u;
             }
-            const uint32_t k0 = t * KT + half * 32;
-            if (k0 + 32 > my_pos + 1 || k0 + 32 > total) {               // causal / end mask (only near the diagonal)
+            const uint32_t k0 = t * KT + part * KP;
+            if (k0 + KP > my_pos + 1 || k0 + KP > total) {               // causal / end mask (only near the diagonal)
 #pragma unroll
-                for (int i = 0; i < 32; i++)
+                for (int i = 0; i < KP; i++)
                     if (k0 + uint32_t(i) > my_pos || k0 + uint32_t(i) >= total) sv[i] = __float_as_uint(-INFINITY);
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            for (int i = 0; i < KP; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            hmax_s[half * QT + r] = mx;
-            group_sync();                                                // the next write of hmax_s comes after group_or below
-            mx = fmaxf(mx, hmax_s[(half ^ 1u) * QT + r]) * scale_log2;   // both halves of a row now hold the same maximum
+            // Two buffers by step parity: another part of a row may already be one step ahead when this one reads.
+            if constexpr (NS > 1) {
+                float* hm = hmax_s + (t & 1) * NS * QT;
+                hm[part * QT + r] = mx;
+                group_sync();
+#pragma unroll
+                for (int p = 0; p < NS; p++) mx = fmaxf(mx, hm[p * QT + r]);
+            }
+            mx *= scale_log2;                                            // the same in all parts of a row
             float alpha = 1.0f;
             bool need = false;
             if (m_run == -INFINITY) { m_run = mx; }                     // nothing accumulated for this row yet
             else if (mx > m_run + RESCALE_THRESHOLD) { alpha = fast_ex2(m_run - mx); m_run = mx; need = true; }
-            float* alpha_t = alpha_s + (t & 1) * QT;     // by step parity: a fast thread may be one step ahead of a slow one
-            if (half == 0) alpha_t[r] = alpha;
             float sum2[2] = {0.0f, 0.0f};
-            uint32_t pk[16];
+            uint32_t pk[KP / 2];
             const float mref = m_run == -INFINITY ? 0.0f : m_run;         // a row whose keys so far are all masked: p = 0
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
+            for (int i = 0; i < KP; i += 2) {
                 const float p0 = fast_ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -mref));
                 const float p1 = fast_ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -mref));
                 sum2[(i >> 1) & 1] += p0 + p1;
                 pk[i / 2] = Elem<T>::pack2(p0, p1);
             }
             l_run = l_run * alpha + (sum2[0] + sum2[1]);
-            const bool any_need = group_or(need || fail);
-            if (any_need && group_or(fail)) { stop = true; break; }
-            wait_w(bar(B_PEMPTY), (t - 1) & 1);          // PV of the previous step complete: O^T stable, P free
+            if (t > 0) wait_w(bar(B_PVDONE + ((t - 1) % S_BUFS)), ((t - 1) / S_BUFS) & 1);   // PV of the previous step complete: this row of O is stable
             if (fail) continue;
             tc_fence_after();
-            if (any_need && t > 0) {
-                // O^T[value dim = this thread's lane][query column] *= alpha[query]; each half takes two of the four chunks
+            // tcgen05.ld / .st are warp-wide: the warp rescales when any of its rows needs it (the others multiply by 1)
+            if (t > 0 && __any_sync(0xffffffffu, need)) {    // O[this row][this part's VP value dims] *= alpha
 #pragma unroll 1
-                for (uint32_t c = 2 * half; c < 2 * half + 2; c++) {
+                for (uint32_t c = 0; c < VP / 32; c++) {
                     uint32_t o[32];
-                    tc_ld32(tmem + lane_base + COL_O + c * 32, o);
+                    tc_ld32(tmem + lane_base + COL_O + part * VP + c * 32, o);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_t[c * 32 + i]);
-                    tc_st32(tmem + lane_base + COL_O + c * 32, o);
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tc_st32(tmem + lane_base + COL_O + part * VP + c * 32, o);
                 }
-                tc_wait_st();
             }
-            {   // row r of the K-major swizzled P tile [128 queries][64 keys]: this half's 4 of the 8 chunks of 16 bytes
-                unsigned char* prow = sm + OFF_P + r * 128;
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-                    *reinterpret_cast<uint4*>(prow + (((half * 4 + j) ^ (r & 7)) << 4)) =
-                        make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_stn(s_addr, pk);              // P over the first half of this thread's own score columns
+            tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(B_PFULL));
         }
-        if (!stop) {
-            wait_w(bar(B_OFULL), 0);
-            lsum_s[half * QT + r] = l_run;
-            const bool bad = group_or(fail);
-            if (half == 0) {
-                const float l = lsum_s[r] + lsum_s[QT + r];
-                linv_s[r] = l > 0.0f ? 1.0f / l : 0.0f;
-            }
-            group_sync();
-            if (!bad) {
-                tc_fence_after();
-                // this thread holds value dim r of every query column: out[query][h][r] = O^T[r][query] / l[query]
-#pragma unroll 1
-                for (uint32_t c = 2 * half; c < 2 * half + 2; c++) {
-                    uint32_t o[32];
-                    tc_ld32(tmem + lane_base + COL_O + c * 32, o);
-                    tc_wait_ld();
+        wait_w(bar(B_OFULL), 0);
+        lsum_s[part * QT + r] = l_run;
+        const bool bad = group_or(fail);
+        if (!bad) {
+            tc_fence_after();
+            float l = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const uint32_t qi = q0 + c * 32 + i;
-                        if (qi < a.n_new)
-                            out[(size_t(a.q_row0 + qi) * a.H + h) * kVDim + r] = Elem<T>::from_f32(__uint_as_float(o[i]) * linv_s[c * 32 + i]);
-                    }
-                }
+            for (int p = 0; p < NS; p++) l += lsum_s[p * QT + r];
+            const float linv = l > 0.0f ? 1.0f / l : 0.0f;
+            uint4* dst = reinterpret_cast<uint4*>(out + (size_t(a.q_row0 + qi) * a.H + h) * kVDim + part * VP);
+#pragma unroll 1
+            for (uint32_t c = 0; c < VP / 32; c++) {
+                uint32_t o[32];
+                tc_ld32(tmem + lane_base + COL_O + part * VP + c * 32, o);
+                tc_wait_ld();
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    w[i] = Elem<T>::pack2(__uint_as_float(o[2 * i]) * linv, __uint_as_float(o[2 * i + 1]) * linv);
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (live) dst[c * 4 + j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
             }
         }
         tc_fence_before();
@@ -404,9 +425,10 @@ int launch_prefill_tc5(int dtype, const void* q, uint32_t q_rows_total, uint32_t
 {
     if (n_new == 0) return 0;
     const uint32_t total = start + n_new;
-    alignas(64) CUtensorMap mq, mk, mv, mr;
-    if (!make_map(&mq, dtype, q, q_rows_total, uint64_t(H) * kQDim, uint64_t(H) * kQDim, QT) ||
-        !make_map(&mk, dtype, kx, total, uint64_t(H) * kNope, uint64_t(H) * kNope, KT) ||
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15u) return int(cudaErrorMisalignedAddress);
+    (void)q_rows_total;
+    alignas(64) CUtensorMap mk, mv, mr;
+    if (!make_map(&mk, dtype, kx, total, uint64_t(H) * kNope, uint64_t(H) * kNope, KT) ||
         !make_map(&mv, dtype, vx, total, uint64_t(H) * kVDim, uint64_t(H) * kVDim, KT) ||
         !make_map(&mr, dtype, latent, total, kRow, kRow, KT))
         return -1;
@@ -414,10 +436,10 @@ int launch_prefill_tc5(int dtype, const void* q, uint32_t q_rows_total, uint32_t
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid((n_new + QT - 1) / QT, H);
     if (dtype == 0)
-        return int(launch_pdl(prefill_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, mq, mk, mv, mr, a,
-                              static_cast<__half*>(out), scale_log2, status));
-    return int(launch_pdl(prefill_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, mq, mk, mv, mr, a,
-                          static_cast<__nv_bfloat16*>(out), scale_log2, status));
+        return int(launch_pdl(prefill_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, static_cast<const __half*>(q),
+                              mk, mv, mr, a, static_cast<__half*>(out), scale_log2, status));
+    return int(launch_pdl(prefill_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st,
+                          static_cast<const __nv_bfloat16*>(q), mk, mv, mr, a, static_cast<__nv_bfloat16*>(out), scale_log2, status));
 }
 
 }  // namespace mla

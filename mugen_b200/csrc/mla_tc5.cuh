@@ -214,6 +214,39 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint
         "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand from tensor memory: row i of A in lane i, two 16-bit elements of K per 32-bit column (element 2c in the low
+// half of column c), so one K = 16 step reads 8 columns starting at a_tmem.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 db;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 bits, repeated along 16 columns: thread i writes lane i, columns 0..15
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// 32 lanes x 32 bits, repeated along 8 columns: thread i writes lane i, columns 0..7
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+// 32 lanes x 32 bits, repeated along 16 columns: thread i receives lane i, columns 0..15
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 // 32 lanes x 32 bits, repeated along 32 columns: thread i receives lane i, columns 0..31
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -250,6 +283,16 @@ __device__ __forceinline__ void tc_ld16x256_x8(uint32_t taddr, uint32_t (&r)[32]
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+// the same by array size
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[16]) { tc_ld16(taddr, r); }
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[32]) { tc_ld32(taddr, r); }
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[64]) {
+    tc_ld32(taddr, reinterpret_cast<uint32_t (&)[32]>(r[0]));
+    tc_ld32(taddr + 32, reinterpret_cast<uint32_t (&)[32]>(r[32]));
+}
+__device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[8]) { tc_st8(taddr, r); }
+__device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[16]) { tc_st16(taddr, r); }
+__device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[32]) { tc_st32(taddr, r); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_ex2(float x) {
