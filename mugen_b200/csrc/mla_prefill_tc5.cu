@@ -18,8 +18,8 @@
 //            read it complete, a V buffer one softmax later
 //   QK       S[128 queries x 64 keys] = Q . K^T          12 x tcgen05.mma M128 N64 K16 (A in tensor memory), three score
 //            tiles in flight
-//   softmax  four threads per query row, 16 keys each (the parts of a row exchange their maxima through shared memory;
-//            four softmax warps per scheduler hide each other's dependent-issue latency): causal mask, log2-domain online
+//   softmax  NS = 2 threads per query row, 32 keys each (the parts of a row exchange their maxima through shared memory;
+//            1, 2 and 4 threads per row measure the same within 2 %, 4 slightly slower): causal mask, log2-domain online
 //            softmax with lazy rescaling (threshold 2^8); P in the storage type goes back into the tensor-memory columns
 //            its scores came from
 //   PV       O[128 queries x 128 value dims] += P . V    4 x tcgen05.mma M128 N128 K16, A = P in tensor memory, B = the
@@ -51,7 +51,7 @@ constexpr int OFF_K = 0, OFF_V = OFF_K + K_STAGES * K_STAGE, OFF_MISC = OFF_V + 
 #ifndef MLA_PREFILL_NS
 #define MLA_PREFILL_NS 2
 #endif
-constexpr int NS = MLA_PREFILL_NS;                     // softmax threads per query row (2 or 4)
+constexpr int NS = MLA_PREFILL_NS;                     // softmax threads per query row (1, 2 or 4)
 constexpr int KP = KT / NS, QP = kQDim / NS, VP = kVDim / NS;   // keys, query dims, value dims per thread of a row
 // hmax: [2 step parities][NS parts][128 rows]; lsum: [NS parts][128 rows]
 constexpr int M_HMAX = 256, M_LSUM = M_HMAX + 2 * NS * QT * 4, M_TMEM = M_LSUM + NS * QT * 4, M_ABORT = M_TMEM + 4, MISC_BYTES = M_TMEM + 64;
@@ -59,7 +59,7 @@ constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;       // + slack for 1 
 constexpr int NUM_SOFTMAX = NS * QT;
 constexpr int FIRST_SOFTMAX_WARP = 3;
 constexpr int NUM_THREADS = 32 * FIRST_SOFTMAX_WARP + NUM_SOFTMAX;
-// tensor memory columns: Q as 16-bit pairs (96), two score tiles (P of a step overwrites the head of each part of its
+// tensor memory columns: Q as 16-bit pairs (96), S_BUFS score tiles (P of a step overwrites the head of each part of its
 // scores), O
 constexpr int S_BUFS = 3;                              // score tiles in flight: QK of step t + 1 never waits for softmax t
 constexpr uint32_t TMEM_COLS = 512, COL_Q = 0, COL_S = 128, COL_O = COL_S + S_BUFS * KT;
