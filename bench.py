@@ -601,8 +601,7 @@ def sub_kv_range(torch, dist, world, rank, local, peak):
     def step(timed=False):
         ctx.step_begin([s], [1 if owner else 0])
         for l in range(L):
-            ctx.step_append(l, kv[l])
-            ctx.step_attend_partial(l, q[l], partial)
+            ctx.step_layer_partial(l, kv[l] if owner else None, q[l], partial)
             exchange(timed)
             ctx.merge_partials(l, world, 1, gathered, out[l])
         ctx.step_end()

@@ -195,6 +195,12 @@ int mla_step_balance(const mla_ctx* ctx, uint32_t* workers, uint32_t* min_pages,
  * to attend emits (-inf, 0, 0). */
 int mla_step_attend_partial(mla_ctx* ctx, uint32_t layer, const void* q, float* partial,
                             void* stream);
+/* The same with the append of the step's new rows done by the same launch that absorbs q (the fused form of
+ * mla_step_append + mla_step_attend_partial, as mla_step_layer is for the unsharded step).  kv_a may be NULL on a
+ * GPU whose shard takes no new row in this step (only the owner of the tail range appends: reference
+ * transformer.cpp:3930-3987 writes one row per layer and step). */
+int mla_step_layer_partial(mla_ctx* ctx, uint32_t layer, const void* kv_a, const void* q, float* partial,
+                           void* stream);
 /* Log-sum-exp merge of n_parts such partials (DEVICE float [n_parts][rows][n_heads][514],
  * e.g. the result of an all-gather) followed by the W_UV projection
  * (transformer.cpp:2610-2620).  out: DEVICE [rows][n_heads][128]. */

@@ -69,6 +69,7 @@ SIGNATURES = {
     "mla_step_end": (C.c_int, [vp]),
     "mla_step_info": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32)]),
     "mla_step_attend_partial": (C.c_int, [vp, u32, vp, vp, vp]),
+    "mla_step_layer_partial": (C.c_int, [vp, u32, vp, vp, vp, vp]),
     "mla_merge_partials": (C.c_int, [vp, u32, u32, u32, vp, vp, vp]),
     "mla_launch_count": (C.c_int, [vp, C.POINTER(u64)]),
     "mla_kernel_name": (C.c_char_p, [vp]),

@@ -103,6 +103,7 @@ struct mla_ctx {
 
     // pages of the last planned step per persistent worker (mla_step_balance)
     uint32_t plan_workers = 0, plan_min_pages = 0, plan_max_pages = 0;
+    uint32_t step_new_rows = 0;     // rows the open step appends (a KV-range shard that does not own the tail has none)
 
     // step state
     bool in_step = false;
@@ -975,6 +976,8 @@ int mla_step_begin(mla_ctx* c, uint32_t n_seq, const uint32_t* seq_ids, const ui
         }
     }
     if (int e = upload_meta(c, seqs, rows, true, st)) return e;
+    c->step_new_rows = 0;
+    for (uint32_t i = 0; i < n_seq; i++) c->step_new_rows += nn[i];
     // table offsets of the step's sequences inside the upload (the prefill path gathers rows through them)
     c->step_tbl_off.resize(n_seq);
     {
@@ -1062,6 +1065,23 @@ int mla_step_attend_partial(mla_ctx* c, uint32_t layer, const void* q, float* pa
     if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_attend_partial outside step_begin/step_end");
     if (int e = check_layer(c, layer, true)) return e;
     return run_attend(c, layer, q, nullptr, partial, static_cast<cudaStream_t>(stream));
+}
+
+int mla_step_layer_partial(mla_ctx* c, uint32_t layer, const void* kv_a, const void* q, float* partial, void* stream)
+{
+    if (!c || !q || !partial) return fail(c, MLA_ERR_INVALID, "null argument");
+    USE_DEVICE(c);
+    if (!c->in_step) return fail(c, MLA_ERR_STATE, "step_layer_partial outside step_begin/step_end");
+    if (int e = check_layer(c, layer, true)) return e;
+    if (c->has_plan_b) return fail(c, MLA_ERR_UNSUPPORTED, "a step with prefill chunks has no partial form");
+    if (c->step_new_rows && !kv_a) return fail(c, MLA_ERR_INVALID, "the step appends rows on this GPU: kv_a is needed");
+    auto st = static_cast<cudaStream_t>(stream);
+    if (!c->step_new_rows) kv_a = nullptr;           // query-only rows: nothing to append, kv_a is never read
+    if (kv_a && !c->layers[layer].has_map) {
+        if (int e = run_append(c, layer, kv_a, st)) return e;
+        kv_a = nullptr;
+    }
+    return run_attend(c, layer, q, nullptr, partial, st, kv_a);
 }
 
 int mla_merge_partials(mla_ctx* c, uint32_t layer, uint32_t n_parts, uint32_t rows, const float* partials,

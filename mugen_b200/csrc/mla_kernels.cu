@@ -226,86 +226,86 @@ void launch_absorb(int dtype, const void* q, const void* w_uk_t, void* q_abs, ui
 //   out[r][h][j] = T( sum_d o_c[d] * W_UV[h*128+j][d] )
 // Parts of row r are either the row's split-KV segments (records seg*H + h, segments
 // row_seg_begin[r] .. row_seg_begin[r+1]) or the shards of a KV-range-sharded sequence (records
-// (p*rows + r)*H + h, p < n_parts).  With `exported` non-null the merged, still un-normalised
-// state is written out instead of being projected.
-// o_c stays in float through the projection (the W_UV product is done on the FP32 pipe): the
-// bf16 error budget has no room for another rounding here.
+// (p*rows + r)*H + h, p < n_parts).
 // ------------------------------------------------------------------------------------------
-template <typename T, int RT>
-__global__ void __launch_bounds__(256)
-merge_outproj_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin,
-                     uint32_t n_parts, const T* __restrict__ w_uv, T* __restrict__ out,
-                     float* __restrict__ exported, uint32_t rows, uint32_t H, const uint32_t* __restrict__ att_row)
+
+// The merged, still un-normalised state of every (row, head) written out (the per-GPU partial of a KV-range-sharded
+// sequence): one block per (head, row); the 16 warps take a slice of the row's parts each (a lane owns dims
+// 64*k + 2*lane (+1), k = 0..7, so a warp load covers whole lines of a record), their sums meet in shared memory and
+// warp 0 folds them.  One sequence cut into 74 segments costs two round trips to memory.
+__global__ void __launch_bounds__(512)
+export_partial_kernel(const float* __restrict__ recs, const uint32_t* __restrict__ row_seg_begin, uint32_t n_parts,
+                      float* __restrict__ exported, uint32_t rows, uint32_t H)
 {
-    __shared__ __align__(16) float oc[RT][kRank];
-    const uint32_t h = blockIdx.x, r0 = blockIdx.y * RT, tid = threadIdx.x;
-    const int d0 = tid * 2;
-    for (int rr = 0; rr < RT; rr++) {
-        const uint32_t r = r0 + rr;
-        float a0 = 0.0f, a1 = 0.0f, L = 0.0f, M = -INFINITY;
-        if (r < rows) {
-            uint32_t pb, pe;
-            if (row_seg_begin) { pb = row_seg_begin[r]; pe = row_seg_begin[r + 1]; }
-            else               { pb = 0; pe = n_parts; }
-            auto rec_of = [&](uint32_t p) -> const float* {
-                const size_t idx = row_seg_begin ? (size_t(p) * H + h)
-                                                 : ((size_t(p) * rows + r) * H + h);
-                return recs + idx * kPart;
-            };
-            for (uint32_t p = pb; p < pe; p++) M = fmaxf(M, rec_of(p)[0]);
-            if (M > -INFINITY) {
-                for (uint32_t p = pb; p < pe; p++) {
-                    const float* rc = rec_of(p);
-                    const float w = exp2f(rc[0] - M);
-                    L = fmaf(w, rc[1], L);
-                    const float2 a = *reinterpret_cast<const float2*>(rc + 2 + d0);
-                    a0 = fmaf(w, a.x, a0);
-                    a1 = fmaf(w, a.y, a1);
+    __shared__ float scratch[16][32][18];
+    const uint32_t h = blockIdx.x, r = blockIdx.y, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    uint32_t pb = 0, pe = n_parts;
+    if (row_seg_begin) { pb = row_seg_begin[r]; pe = row_seg_begin[r + 1]; }
+    auto rec_of = [&](uint32_t p) -> const float* {
+        const size_t idx = row_seg_begin ? (size_t(p) * H + h) : ((size_t(p) * rows + r) * H + h);
+        return recs + idx * kPart;
+    };
+    const uint32_t chunk = (pe - pb + 15) / 16;
+    pb = min(pe, pb + warp * chunk);
+    pe = min(pe, pb + chunk);
+    float M = -INFINITY, L = 0.0f, acc[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) acc[k] = 0.0f;
+    for (uint32_t p = pb; p < pe; p += 4) {
+        float2 ml[4], v[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const bool on = p + i < pe;
+            const float* rc = rec_of(on ? p + i : pb);
+            ml[i] = on ? *reinterpret_cast<const float2*>(rc) : make_float2(-INFINITY, 0.0f);
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                v[i][k] = on ? *reinterpret_cast<const float2*>(rc + 2 + 64 * k + 2 * lane) : make_float2(0.0f, 0.0f);
+        }
+        const float Mn = fmaxf(fmaxf(M, ml[0].x), fmaxf(fmaxf(ml[1].x, ml[2].x), ml[3].x));
+        if (Mn > -INFINITY) {
+            const float sc = exp2f(M - Mn);
+            L *= sc;
+#pragma unroll
+            for (int k = 0; k < 16; k++) acc[k] *= sc;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float w = exp2f(ml[i].x - Mn);
+                L = fmaf(w, ml[i].y, L);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    acc[2 * k] = fmaf(w, v[i][k].x, acc[2 * k]);
+                    acc[2 * k + 1] = fmaf(w, v[i][k].y, acc[2 * k + 1]);
                 }
             }
-            if (exported) {
-                float* ex = exported + (size_t(r) * H + h) * kPart;
-                if (tid == 0) { ex[0] = M; ex[1] = L; }
-                *reinterpret_cast<float2*>(ex + 2 + d0) = make_float2(a0, a1);
-            }
+            M = Mn;
         }
-        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-        oc[rr][d0] = a0 * inv;
-        oc[rr][d0 + 1] = a1 * inv;
     }
-    if (exported) return;
+    float* mine = scratch[warp][lane];
+    mine[0] = M;
+    mine[1] = L;
+#pragma unroll
+    for (int k = 0; k < 16; k++) mine[2 + k] = acc[k];
     __syncthreads();
-    const int warp = tid / 32, lane = tid % 32;
-    for (int jj = 0; jj < kVDim / 8; jj++) {
-        const int j = warp * (kVDim / 8) + jj;
-        const T* wrow = w_uv + (size_t(h) * kVDim + j) * kRank;
-        float s[RT];
+    if (warp != 0) return;
+    M = -INFINITY;
+    L = 0.0f;
 #pragma unroll
-        for (int rr = 0; rr < RT; rr++) s[rr] = 0.0f;
+    for (int k = 0; k < 16; k++) acc[k] = 0.0f;
+    for (int j = 0; j < 16; j++) {
+        const float* o = scratch[j][lane];
+        const float Mj = o[0];
+        if (Mj == -INFINITY) continue;
+        const float Mn = fmaxf(M, Mj), sc = exp2f(M - Mn), w = exp2f(Mj - Mn);
+        L = fmaf(w, o[1], L * sc);
 #pragma unroll
-        for (int k = 0; k < kRank / 64; k++) {
-            const typename Elem<T>::pair w2 =
-                *reinterpret_cast<const typename Elem<T>::pair*>(wrow + k * 64 + lane * 2);
-            const float w0 = Elem<T>::to_f32(w2.x), w1 = Elem<T>::to_f32(w2.y);
-#pragma unroll
-            for (int rr = 0; rr < RT; rr++) {
-                const float2 o = *reinterpret_cast<const float2*>(&oc[rr][k * 64 + lane * 2]);
-                s[rr] = fmaf(o.x, w0, s[rr]);
-                s[rr] = fmaf(o.y, w1, s[rr]);
-            }
-        }
-#pragma unroll
-        for (int rr = 0; rr < RT; rr++) {
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) s[rr] += __shfl_xor_sync(0xffffffffu, s[rr], off);
-        }
-        if (lane < RT && r0 + lane < rows) {
-            float v = 0.0f;
-#pragma unroll
-            for (int rr = 0; rr < RT; rr++) v = (lane == rr) ? s[rr] : v;
-            out[(size_t(att_row ? att_row[r0 + lane] : r0 + lane) * H + h) * kVDim + j] = Elem<T>::from_f32(v);
-        }
+        for (int k = 0; k < 16; k++) acc[k] = fmaf(w, o[2 + k], acc[k] * sc);
+        M = Mn;
     }
+    float* ex = exported + (size_t(r) * H + h) * kPart;
+    if (lane == 0) { ex[0] = M; ex[1] = L; }
+#pragma unroll
+    for (int k = 0; k < 8; k++) *reinterpret_cast<float2*>(ex + 2 + 64 * k + 2 * lane) = make_float2(acc[2 * k], acc[2 * k + 1]);
 }
 
 // Same merge, projection on the warp-level tensor path.  Block = (head, group of up to 4 row tiles
@@ -468,16 +468,7 @@ void launch_merge(int dtype, const float* recs, const uint32_t* row_seg_begin, u
                 static_cast<__nv_bfloat16*>(out), rows, H, att_row);
         return;
     }
-    constexpr int RT = 8;
-    dim3 grid(H, (rows + RT - 1) / RT);
-    if (dtype == 0)
-        merge_outproj_kernel<__half, RT><<<grid, 256, 0, st>>>(
-            recs, row_seg_begin, n_parts, static_cast<const __half*>(w_uv),
-            static_cast<__half*>(out), exported, rows, H, att_row);
-    else
-        merge_outproj_kernel<__nv_bfloat16, RT><<<grid, 256, 0, st>>>(
-            recs, row_seg_begin, n_parts, static_cast<const __nv_bfloat16*>(w_uv),
-            static_cast<__nv_bfloat16*>(out), exported, rows, H, att_row);
+    export_partial_kernel<<<dim3(H, rows), 512, 0, st>>>(recs, row_seg_begin, n_parts, exported, rows, H);
 }
 
 }  // namespace mla

@@ -117,16 +117,29 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     constexpr bool small = kSmall;                        // chosen at launch: the whole step has at most 16 rows
     float acc_s[kSmall ? 16 : 1], inv_s = 0.0f;
     if constexpr (kSmall) {
+        // With fewer than nine rows the idle warps share a row's parts: G warps per row sweep a slice each and one of
+        // them folds the G partial sums afterwards (one sequence cut into 74 segments: 2 round trips to memory, not 19).
+        const uint32_t nrows = min(rows - r0, 16u);
+        uint32_t G = 1;
+        while (2 * G * nrows <= 16u) G *= 2;
+        const uint32_t myrow = warp / G, g = warp % G, rw = r0 + myrow;
+        uint32_t pb = 0, pe = 0;
+        if (myrow < nrows) {
+            if (row_seg_begin) { pb = row_seg_begin[rw]; pe = row_seg_begin[rw + 1]; }
+            else               { pe = n_parts; }
+            const uint32_t chunk = (pe - pb + G - 1) / G;
+            pb = min(pe, pb + g * chunk);
+            pe = min(pe, pb + chunk);
+        }
         float M = -INFINITY, L = 0.0f;
 #pragma unroll
         for (int k = 0; k < 16; k++) acc_s[k] = 0.0f;
-        const uint32_t rw = r0 + warp;
-        for (uint32_t p = pb4[0]; p < pe4[0]; p += 4) {
+        for (uint32_t p = pb; p < pe; p += 4) {
             float2 ml[4], v[4][8];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const bool on = p + i < pe4[0];
-                const float* rc = rec_of(rw, on ? p + i : pb4[0]);
+                const bool on = p + i < pe;
+                const float* rc = rec_of(rw, on ? p + i : pb);
                 ml[i] = on ? *reinterpret_cast<const float2*>(rc) : make_float2(-INFINITY, 0.0f);
 #pragma unroll
                 for (int k = 0; k < 8; k++)
@@ -150,6 +163,32 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
                 }
                 M = Mn;
             }
+        }
+        if (G > 1) {        // block-uniform.  The operand buffers are free until the sums are written there below.
+            float* scratch = reinterpret_cast<float*>(sm + OFF_AHI);
+            float* mine = scratch + (size_t(warp) * 32 + lane) * 18;
+            mine[0] = M;
+            mine[1] = L;
+#pragma unroll
+            for (int k = 0; k < 16; k++) mine[2 + k] = acc_s[k];
+            __syncthreads();
+            M = -INFINITY;
+            L = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; k++) acc_s[k] = 0.0f;
+            if (warp < nrows) {                          // from here on warp w stands for row w, as the operand writes expect
+                for (uint32_t j = 0; j < G; j++) {
+                    const float* o = scratch + (size_t(warp * G + j) * 32 + lane) * 18;
+                    const float Mj = o[0];
+                    if (Mj == -INFINITY) continue;       // warp-uniform: a slice without parts
+                    const float Mn = fmaxf(M, Mj), sc = exp2f(M - Mn), w = exp2f(Mj - Mn);
+                    L = fmaf(w, o[1], L * sc);
+#pragma unroll
+                    for (int k = 0; k < 16; k++) acc_s[k] = fmaf(w, o[2 + k], acc_s[k] * sc);
+                    M = Mn;
+                }
+            }
+            __syncthreads();
         }
         inv_s = L > 0.0f ? 1.0f / L : 0.0f;
     }

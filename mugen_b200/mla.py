@@ -194,6 +194,11 @@ class MlaContext:
         self._check(self.lib.mla_step_attend_partial(self.h, layer, self._dev(q), self._dev(partial),
                                                      self._stream()))
 
+    def step_layer_partial(self, layer: int, kv_a, q, partial) -> None:
+        """Append (kv_a may be None on a GPU whose shard takes no new row) and partial attend in one call."""
+        self._check(self.lib.mla_step_layer_partial(self.h, layer, self._dev(kv_a) if kv_a is not None else None,
+                                                    self._dev(q), self._dev(partial), self._stream()))
+
     def merge_partials(self, layer: int, n_parts: int, rows: int, partials, out) -> None:
         self._check(self.lib.mla_merge_partials(self.h, layer, n_parts, rows, self._dev(partials),
                                                 self._dev(out), self._stream()))

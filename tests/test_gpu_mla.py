@@ -467,10 +467,12 @@ def test_prefill_chunks_take_the_expanded_path(torch, oracle, H, dt, spec, q_rop
     ctx.close()
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("kernel", KERNELS)
-def test_kv_range_shards_merge(torch, oracle, kernel):
+def test_kv_range_shards_merge(torch, oracle, kernel, fused):
     """One sequence cut into 3 KV ranges held by 3 contexts (stand-ins for 3 GPUs): each emits
-    (m, l, acc) partials; the merged + projected result equals the unsharded CPU result."""
+    (m, l, acc) partials; the merged + projected result equals the unsharded CPU result.  `fused`: the append rides in
+    the launch that absorbs q (mla_step_layer_partial; the shards without a new row pass no kv_a)."""
     H, dt, S = 32, synth.DT_BF16, 64 * 9 + 17
     case = synth.make_layer_case(71, H, [S], dt)
     cuts = [0, 64 * 3, 64 * 6, S]
@@ -493,8 +495,11 @@ def test_kv_range_shards_merge(torch, oracle, kernel):
         ctx.advance_seq_len(s, n)
         # the shard owning the tail takes the appended token; the others only answer the query
         ctx.step_begin([s], [1 if g == 2 else 0])
-        ctx.step_append(0, _dev(torch, kv_a))
-        ctx.step_attend_partial(0, q, parts[g])
+        if fused:
+            ctx.step_layer_partial(0, _dev(torch, kv_a) if g == 2 else None, q, parts[g])
+        else:
+            ctx.step_append(0, _dev(torch, kv_a))
+            ctx.step_attend_partial(0, q, parts[g])
         ctx.step_end()
         if g == 2:
             assert np.array_equal(ctx.read_rows(0, s, n, 1)[0], new_row[0])
