@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmugen_mla.so")
-SOURCES = ["mla_api.cu", "mla_kernels.cu", "mla_decode_mma.cu", "mla_decode_tc5.cu", "mla_decode_tc5_pair2.cu", "mla_merge_tc5.cu", "mla_absorb_tc5.cu", "mla_noalloc.cu", "mla_selftest.cu", "mla_gguf.cu", "mla_gemm_tc5.cu", "mla_prefill_tc5.cu"]
+SOURCES = ["mla_api.cu", "mla_kernels.cu", "mla_decode_mma.cu", "mla_decode_tc5.cu", "mla_decode_tc5_pair2.cu", "mla_decode_tc5_t16.cu", "mla_merge_tc5.cu", "mla_absorb_tc5.cu", "mla_noalloc.cu", "mla_selftest.cu", "mla_gguf.cu", "mla_gemm_tc5.cu", "mla_prefill_tc5.cu"]
 HEADERS = ["mla_common.cuh", "mla_launch.h", "mla_tc5.cuh", "../host/page_table.hpp", "../host/rope_table.hpp", "../host/gguf_reader.hpp",
            "../../include/mugen_mla.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",

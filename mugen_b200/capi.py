@@ -18,7 +18,7 @@ ERR_NAMES = {1: "INVALID", 2: "CUDA", 3: "NO_PAGES", 4: "CAPACITY", 5: "STATE", 
              7: "UNSUPPORTED"}
 DTYPE_F16, DTYPE_BF16 = 0, 1
 W_F16, W_Q4_0, W_Q8_0, W_BF16 = 1, 2, 8, 30
-KERNEL_AUTO, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR128 = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR128, KERNEL_TCGEN05_T16 = 0, 1, 2, 3, 4
 
 
 class MlaConfig(C.Structure):

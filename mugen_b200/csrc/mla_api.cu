@@ -405,6 +405,8 @@ int run_attend(mla_ctx* c, uint32_t layer, const void* q, void* out, float* expo
                                            c->status_dev, st);
     else if (c->kernel == MLA_KERNEL_TCGEN05)
         e = mla::launch_decode_tc5(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
+    else if (c->kernel == MLA_KERNEL_TCGEN05_T16)
+        e = mla::launch_decode_tc5_t16(int(c->cfg.dtype), c->tmaps, layer, c->cfg.n_pages, m, c->recs, H, c->status_dev, st);
     else
         e = mla::launch_decode_mma(int(c->cfg.dtype), c->q_abs, layer_pool(c, layer), c->cfg.n_pages, m,
                                    c->recs, H, c->status_dev, st);
@@ -592,6 +594,8 @@ int make_tensor_maps(mla_ctx* c)
         const cuuint64_t qstrides[2] = {cuuint64_t(mla::kRow) * 2, 128};
         const cuuint32_t qbox[3] = {64, 64, 9};
         if (int e = encode(mla::kMapQueries, "absorbed queries", 3, c->q_abs, qdims, qstrides, qbox)) return e;
+        const cuuint32_t qbox16[3] = {64, 16, 9};
+        if (int e = encode(mla::kMapQueries16, "absorbed queries, 16 heads", 3, c->q_abs, qdims, qstrides, qbox16)) return e;
     }
     return MLA_OK;
 }
@@ -615,7 +619,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (cfg->page_tokens != 64) return fail(nullptr, MLA_ERR_UNSUPPORTED, "page_tokens must be 64");
     if (cfg->n_pages == 0 || cfg->max_seqs == 0) return fail(nullptr, MLA_ERR_INVALID, "n_pages and max_seqs must be > 0");
     if (cfg->dtype > MLA_DTYPE_BF16) return fail(nullptr, MLA_ERR_INVALID, "dtype must be MLA_DTYPE_F16 or MLA_DTYPE_BF16");
-    if (cfg->kernel > MLA_KERNEL_TCGEN05_PAIR128) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
+    if (cfg->kernel > MLA_KERNEL_TCGEN05_T16) return fail(nullptr, MLA_ERR_INVALID, "unknown kernel selector");
 
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
@@ -644,14 +648,15 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (prop.major != 10)
         { cp->err = "this library is built for sm_100a only; device is sm_" + std::to_string(prop.major * 10 + prop.minor);
           return bail(MLA_ERR_UNSUPPORTED); }
-    // 128-head groups go to the SM-pair kernel, other wide head counts fill the 64-row tcgen05
-    // tiles of the single-block kernel, narrow ones map 1:1 onto m16n8k16
+    // 128-head groups go to the SM-pair kernel, other wide head counts fill the 64-row tcgen05 tiles of the
+    // single-block kernel, narrow ones take the transposed tcgen05 form (tokens as rows, 16 heads as columns)
     c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
               : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
-              : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_MMA;
+              : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_TCGEN05_T16;
     const uint32_t H = cfg->n_heads;
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));
+    else if (c->kernel == MLA_KERNEL_TCGEN05_T16) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 15) / 16));
     else c->workers = std::max<uint32_t>(1, c->sm_count * 2 / ((H + 15) / 16));
 
     c->pt = std::make_unique<PageTable>(cfg->page_tokens, cfg->n_pages, cfg->max_seqs, cfg->max_seq_len);
@@ -725,6 +730,13 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
         if (int rc = make_tensor_maps(cp)) return bail(rc);
         if (int ce = mla::decode_tc5_configure()) {
             cp->err = std::string("tcgen05 kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
+            return bail(MLA_ERR_CUDA);
+        }
+    }
+    if (c->kernel == MLA_KERNEL_TCGEN05_T16) {
+        if (int rc = make_tensor_maps(cp)) return bail(rc);
+        if (int ce = mla::decode_tc5_t16_configure()) {
+            cp->err = std::string("tcgen05 16-head kernel configuration: ") + cudaGetErrorString(cudaError_t(ce));
             return bail(MLA_ERR_CUDA);
         }
     }
@@ -1287,7 +1299,8 @@ int mla_profile_read(mla_ctx* c, uint32_t* launches, float* total_ms)
 const char* mla_kernel_name(const mla_ctx* c)
 {
     if (!c) return "";
-    return c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? "tcgen05-pair128" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05" : "mma";
+    return c->kernel == MLA_KERNEL_TCGEN05_PAIR128 ? "tcgen05-pair128" : c->kernel == MLA_KERNEL_TCGEN05 ? "tcgen05"
+         : c->kernel == MLA_KERNEL_TCGEN05_T16 ? "tcgen05-t16" : "mma";
 }
 
 int mla_read_rows(mla_ctx* c, uint32_t layer, uint32_t id, uint32_t row_begin, uint32_t n, void* host_out, void* stream)

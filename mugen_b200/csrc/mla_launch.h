@@ -30,13 +30,20 @@ int launch_decode_tc5(int dtype, const void* tmaps, uint32_t layer, uint32_t n_p
                       float* recs, uint32_t H, uint32_t* status, cudaStream_t st);
 int decode_tc5_configure();   // sets the kernel's attributes on the current device
 
+// The transposed form for narrow head counts (mla_decode_tc5_t16.cu): tokens are the M rows, groups of 16 heads the N
+// columns; grid (persistent blocks, ceil(H/16)).  Uses kMapPoolPage and kMapQueries16.
+int launch_decode_tc5_t16(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m, float* recs,
+                          uint32_t H, uint32_t* status, cudaStream_t st);
+int decode_tc5_t16_configure();
+
 // Tensor maps a context builds once (mla_api.cu, make_tensor_maps), by index into its array.
 enum : int {
     kMapPoolSub = 0,      // cache pool [layers][slots][576]: box 64 values x 64 tokens (one K sub-tile)
     kMapPoolV = 1,        // cache pool, whole-row view (64 values, slots, 9 chunks, layers): box 64 tokens x 2 chunks
     kMapQueries = 2,      // absorbed queries, whole-row view: box 64 head rows x 9 chunks
     kMapPoolPage = 3,     // cache pool, whole-row view: box 64 tokens x 9 chunks (one page in one instruction)
-    kMapCount = 4
+    kMapQueries16 = 4,    // absorbed queries, whole-row view: box 16 head rows x 9 chunks
+    kMapCount = 5
 };
 
 // The same on a pair of SMs (cluster of 2, tcgen05.mma.cta_group::2), 128-token tiles (two pages per score

@@ -13,16 +13,17 @@
 // One block per (tile of 128 query tokens, head); the whole tile state lives in tensor memory:
 //   Q        [128 queries][192 dims] written once into tensor memory by the softmax threads (row = lane, two dims per
 //            column) and used as the A operand of every score MMA: no shared-memory reads for it
-//   TMA      per 64-token step K [64][192] (two boxes of expanded nope dims + one box of rope dims straight from the
-//            gathered latent rows) and V [64][128], rings of four each; a K buffer is free as soon as the score MMAs that
-//            read it complete, a V buffer one softmax later
-//   QK       S[128 queries x 64 keys] = Q . K^T          12 x tcgen05.mma M128 N64 K16 (A in tensor memory), three score
-//            tiles in flight
-//   softmax  NS = 2 threads per query row, 32 keys each (the parts of a row exchange their maxima through shared memory;
+//   TMA      per step of KT = 128 keys K [128][192] (two boxes of expanded nope dims + one box of rope dims straight from
+//            the gathered latent rows) and V [128][128], rings of two each; a K buffer is free as soon as the score MMAs
+//            that read it complete, a V buffer one softmax later
+//   QK       S[128 queries x 128 keys] = Q . K^T         12 x tcgen05.mma M128 N128 K16 (A in tensor memory), two score
+//            tiles in flight (steps of 64 keys with rings of four and three score tiles measure 13 % slower: the fixed
+//            cost of a step - waits, the exchange of the maxima, the hand-over to the PV issuer - is paid per step)
+//   softmax  NS = 2 threads per query row, 64 keys each (the parts of a row exchange their maxima through shared memory;
 //            1, 2 and 4 threads per row measure the same within 2 %, 4 slightly slower): causal mask, log2-domain online
 //            softmax with lazy rescaling (threshold 2^8); P in the storage type goes back into the tensor-memory columns
 //            its scores came from
-//   PV       O[128 queries x 128 value dims] += P . V    4 x tcgen05.mma M128 N128 K16, A = P in tensor memory, B = the
+//   PV       O[128 queries x 128 value dims] += P . V    8 x tcgen05.mma M128 N128 K16, A = P in tensor memory, B = the
 //            staged V tile read MN-major (no transpose)
 //   rescale  a row whose maximum moved rescales its own O row (its own lane) after the previous PV completes; no
 //            block-wide agreement is needed
@@ -43,10 +44,13 @@ namespace {
 
 using namespace tc5;
 
-constexpr int QT = 128, KT = 64;
-constexpr int K_SUB = KT * 128;                        // 8,192:  [64 keys][64 dims]
-constexpr int K_STAGE = 3 * K_SUB, V_STAGE = 2 * K_SUB;        // K: 192 dims, V: 128 dims of 64 keys
-constexpr int K_STAGES = 4, V_STAGES = 4;
+#ifndef MLA_PREFILL_KT
+#define MLA_PREFILL_KT 128
+#endif
+constexpr int QT = 128, KT = MLA_PREFILL_KT;           // queries per block, keys per step (64 or 128)
+constexpr int K_SUB = KT * 128;                        // [KT keys][64 dims]
+constexpr int K_STAGE = 3 * K_SUB, V_STAGE = 2 * K_SUB;        // K: 192 dims, V: 128 dims of KT keys
+constexpr int K_STAGES = KT == 64 ? 4 : 2, V_STAGES = KT == 64 ? 4 : 2;
 constexpr int OFF_K = 0, OFF_V = OFF_K + K_STAGES * K_STAGE, OFF_MISC = OFF_V + V_STAGES * V_STAGE;
 #ifndef MLA_PREFILL_NS
 #define MLA_PREFILL_NS 2
@@ -61,7 +65,7 @@ constexpr int FIRST_SOFTMAX_WARP = 3;
 constexpr int NUM_THREADS = 32 * FIRST_SOFTMAX_WARP + NUM_SOFTMAX;
 // tensor memory columns: Q as 16-bit pairs (96), S_BUFS score tiles (P of a step overwrites the head of each part of its
 // scores), O
-constexpr int S_BUFS = 3;                              // score tiles in flight: QK of step t + 1 never waits for softmax t
+constexpr int S_BUFS = KT == 64 ? 3 : 2;                              // score tiles in flight: QK of step t + 1 never waits for softmax t
 constexpr uint32_t TMEM_COLS = 512, COL_Q = 0, COL_S = 128, COL_O = COL_S + S_BUFS * KT;
 static_assert(COL_O + kVDim <= TMEM_COLS, "tensor memory columns");
 constexpr float RESCALE_THRESHOLD = 8.0f;

@@ -293,6 +293,13 @@ __device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[64]) {
 __device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[8]) { tc_st8(taddr, r); }
 __device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[16]) { tc_st16(taddr, r); }
 __device__ __forceinline__ void tc_stn(uint32_t taddr, const uint32_t (&r)[32]) { tc_st32(taddr, r); }
+// the same shape, two blocks (16 columns): registers 4k..4k+3 as above for k = 0, 1
+__device__ __forceinline__ void tc_ld16x256_x2(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_ex2(float x) {

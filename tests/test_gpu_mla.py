@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 MAX_ABS, REL_L2 = 2e-2, 5e-3
 YARN = dict(rope_theta=10000.0, rope_scaling_factor=40.0, rope_original_ctx=4096, rms_norm_eps=1e-6)
 
-KERNELS = [capi.KERNEL_MMA, capi.KERNEL_TCGEN05, capi.KERNEL_TCGEN05_PAIR128]
+KERNELS = [capi.KERNEL_MMA, capi.KERNEL_TCGEN05, capi.KERNEL_TCGEN05_PAIR128, capi.KERNEL_TCGEN05_T16]
 if os.environ.get("MLA_TEST_KERNELS"):
     KERNELS = [int(k) for k in os.environ["MLA_TEST_KERNELS"].split(",")]
 
