@@ -49,9 +49,9 @@ enum { MLA_DTYPE_F16 = 0, MLA_DTYPE_BF16 = 1 };
 enum { MLA_W_F16 = 1, MLA_W_Q4_0 = 2, MLA_W_Q8_0 = 8, MLA_W_BF16 = 30 };
 
 /* Split-KV attention kernel family (mla_config.kernel).  AUTO picks PAIR128 when n_heads is a multiple of
- * 128 (SM pairs, tcgen05.mma.cta_group::2, 128-token tiles), TCGEN05 for other head counts >= 64 (one SM per
- * 64 heads) and TCGEN05_T16 below that (tcgen05 in the transposed form: the tokens of a page are the rows of
- * the tile, groups of 16 heads its columns).  MMA (mma.sync m16n8k16, any head count) stays selectable.  All give
+ * 128 (SM pairs, tcgen05.mma.cta_group::2, 128-token tiles), TCGEN05_T16 up to 16 heads (tcgen05 in the
+ * transposed form: the tokens of a page are the rows of the tile, groups of 16 heads its columns) and TCGEN05 for
+ * every other head count (one SM per group of up to 64 heads).  MMA (mma.sync m16n8k16, any head count) stays selectable.  All give
  * the same results within the attention tolerance; each is bit-reproducible from run to run. */
 enum { MLA_KERNEL_AUTO = 0, MLA_KERNEL_MMA = 1, MLA_KERNEL_TCGEN05 = 2, MLA_KERNEL_TCGEN05_PAIR128 = 3,
        MLA_KERNEL_TCGEN05_T16 = 4 };

@@ -648,11 +648,13 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     if (prop.major != 10)
         { cp->err = "this library is built for sm_100a only; device is sm_" + std::to_string(prop.major * 10 + prop.minor);
           return bail(MLA_ERR_UNSUPPORTED); }
-    // 128-head groups go to the SM-pair kernel, other wide head counts fill the 64-row tcgen05 tiles of the
-    // single-block kernel, narrow ones take the transposed tcgen05 form (tokens as rows, 16 heads as columns)
+    // 128-head groups go to the SM-pair kernel; up to 16 heads take the transposed tcgen05 form (tokens as rows, the
+    // heads as 16 columns); everything between fills (part of) the 64-row tiles of the single-block kernel, which
+    // streams the cache once per 64 heads (measured at 32 heads, 64 sequences x 8192 tokens: 124 us against 186 us for
+    // two passes of the 16-column form and 300 us for mma.sync)
     c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
               : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
-              : cfg->n_heads >= 64 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_TCGEN05_T16;
+              : cfg->n_heads > 16 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_TCGEN05_T16;
     const uint32_t H = cfg->n_heads;
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));

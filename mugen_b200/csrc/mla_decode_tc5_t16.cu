@@ -39,7 +39,8 @@ constexpr int NSUB = kRow / 64;                   // 9 sub-tiles of 64 dims
 constexpr int SUB_BYTES = TILE * 128;             // 8 KB
 constexpr int KV_STAGE_BYTES = NSUB * SUB_BYTES;  // 73,728
 constexpr int KV_STAGES = 2;
-constexpr int PREFETCH_TILES = 4;                 // L2 prefetch distance of the producer, in tiles
+// No L2 prefetch ahead of the loads: measured on 16 heads x 32 sequences x 8192 tokens, prefetching 4 / 8 pages ahead
+// (tensor-map or linear) takes the kernel from 59 us to 77 / 88 us.
 constexpr int Q_SUB = HG * 128;                   // 2,048: [16 heads][64 dims]
 constexpr int Q_BYTES = NSUB * Q_SUB;             // 18,432
 constexpr int P_BYTES = HG * 128;                 // 2,048: [16 heads][64 tok]
@@ -146,14 +147,8 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_c
                 mbar_expect_tx(bar(B_QFULL), Q_BYTES);
                 tma_load_3d(sQ, &map_q, bar(B_QFULL), 0, int(s.row * H + h0), 0);          // all 9 sub-tiles in one box
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
-                auto prefetch_tile = [&](uint32_t jj) {
-                    const uint32_t pg = tbl[s.page_begin + jj];
-                    if (pg < n_pages) tma_prefetch_4d(&map_kv, 0, int(pg * kPage), 0, int(layer));
-                };
-                for (uint32_t jj = 0; jj < min(uint32_t(PREFETCH_TILES), s.n_tiles); jj++) prefetch_tile(jj);
                 for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
                     const uint32_t st = t % KV_STAGES;
-                    if (j + PREFETCH_TILES < s.n_tiles) prefetch_tile(j + PREFETCH_TILES);
                     ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     uint32_t page = tbl[s.page_begin + j];
