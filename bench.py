@@ -64,7 +64,7 @@ def parse_args():
     p.add_argument("--ctx", type=int, default=16384)
     p.add_argument("--heads", type=int, default=128)
     p.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
-    p.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05", "tcgen05-pair128"])
+    p.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05", "tcgen05-pair128", "tcgen05-t16"])
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--no-extras", action="store_true", help="skip the kv_range / ragged / v2lite / prefill sub-objects")
@@ -283,7 +283,8 @@ def run_ours(a):
     H, L = a.heads, a.layers
     dt = synth.DT_BF16 if a.dtype == "bf16" else synth.DT_F16
     tdt = torch.bfloat16 if a.dtype == "bf16" else torch.float16
-    kernel = {"auto": capi.KERNEL_AUTO, "mma": capi.KERNEL_MMA, "tcgen05": capi.KERNEL_TCGEN05, "tcgen05-pair128": capi.KERNEL_TCGEN05_PAIR128}[a.kernel]
+    kernel = {"auto": capi.KERNEL_AUTO, "mma": capi.KERNEL_MMA, "tcgen05": capi.KERNEL_TCGEN05, "tcgen05-pair128": capi.KERNEL_TCGEN05_PAIR128,
+              "tcgen05-t16": capi.KERNEL_TCGEN05_T16}[a.kernel]
     total_steps = a.warmup + a.steps + (0 if a.no_e2e else a.warmup + a.steps)
     start_len = a.ctx - 1 - a.warmup          # the first timed step attends exactly ctx rows
     pages_per_seq = (start_len + total_steps + 64 + 63) // 64
