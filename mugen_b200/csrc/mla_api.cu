@@ -650,7 +650,7 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
           return bail(MLA_ERR_UNSUPPORTED); }
     // 128-head groups go to the SM-pair kernel; up to 16 heads take the transposed tcgen05 form (tokens as rows, the
     // heads as 16 columns); everything between fills (part of) the 64-row tiles of the single-block kernel, which
-    // streams the cache once per 64 heads (measured at 32 heads, 64 sequences x 8192 tokens: 124 us against 186 us for
+    // streams the cache once per 64 heads (measured at 32 heads, 64 sequences x 8192 tokens: 128 us against 186 us for
     // two passes of the 16-column form and 300 us for mma.sync)
     c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
               : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
