@@ -118,10 +118,17 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     float acc_s[kSmall ? 16 : 1], inv_s = 0.0f;
     if constexpr (kSmall) {
         // With fewer than nine rows the idle warps share a row's parts: G warps per row sweep a slice each and one of
-        // them folds the G partial sums afterwards (one sequence cut into 74 segments: 2 round trips to memory, not 19).
+        // them folds the G partial sums afterwards (one sequence cut into 74 segments: 3 round trips to memory, not 19)
+        // (only when a row has many parts: with ~10 parts per row, 8 sequences per GPU, the exchange costs more than the
+        // shorter sweep saves: 56.5 against 55.9 us per layer-step)
         const uint32_t nrows = min(rows - r0, 16u);
+        uint32_t max_parts = n_parts;
+        if (row_seg_begin) {
+            max_parts = 0;
+            for (uint32_t i = 0; i < nrows; i++) max_parts = max(max_parts, row_seg_begin[r0 + i + 1] - row_seg_begin[r0 + i]);
+        }
         uint32_t G = 1;
-        while (2 * G * nrows <= 16u) G *= 2;
+        while (2 * G * nrows <= 16u && max_parts >= 12u * G) G *= 2;     // at least six parts per warp
         const uint32_t myrow = warp / G, g = warp % G, rw = r0 + myrow;
         uint32_t pb = 0, pe = 0;
         if (myrow < nrows) {
