@@ -59,7 +59,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     volatile int* fail_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_FAIL);
 
     const uint32_t h = blockIdx.x, tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const uint32_t r0 = blockIdx.y * MT;
+    const uint32_t r0 = blockIdx.y * (kSmall ? 16u : uint32_t(MT));    // small form: 16 rows per block, one per warp
     auto rec_of = [&](uint32_t r, uint32_t p) -> const float* {
         const size_t idx = row_seg_begin ? (size_t(p) * H + h) : ((size_t(p) * rows + r) * H + h);
         return recs + idx * kPart;
@@ -114,7 +114,7 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
     // ONCE for all 512 dims (a lane owns dims 64*k + 2*lane (+1), k = 0..7), so a row of ~10 parts costs three round
     // trips to memory instead of six; the two halves of the projection then only differ in which eight of the lane's
     // sixteen sums they write as operands.
-    constexpr bool small = kSmall;                        // chosen at launch: the whole step has at most 16 rows
+    constexpr bool small = kSmall;                        // chosen at launch: few rows, or few heads (see the launcher)
     float acc_s[kSmall ? 16 : 1], inv_s = 0.0f;
     if constexpr (kSmall) {
         // With fewer than nine rows the idle warps share a row's parts: G warps per row sweep a slice each and one of
@@ -318,12 +318,13 @@ merge_outproj_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const float*
         if (ok) {
             tc_fence_after();
             const uint32_t row = r0 + 16 * warp + lane;
+            const uint32_t row_end = kSmall ? min(rows, r0 + 16u) : rows;       // small form: rows 16.. of the tile are not this block's
 #pragma unroll 1
             for (int c = 0; c < kVDim / 32; c++) {
                 uint32_t o[32];
                 tc_ld32(tmem + ((warp * 32u) << 16) + c * 32, o);
                 tc_wait_ld();
-                if (lane < 16 && row < rows) {
+                if (lane < 16 && row < row_end) {
                     uint4* dst = reinterpret_cast<uint4*>(out + (size_t(att_row ? att_row[row] : row) * H + h) * kVDim + c * 32);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
@@ -372,11 +373,14 @@ int launch_merge_tc5(int dtype, const float* recs, const uint32_t* row_seg_begin
 {
     if (rows == 0) return 0;
     const CUtensorMap* map = static_cast<const CUtensorMap*>(w_map);
-    dim3 grid(H, (rows + MT - 1) / MT);
+    // The small form (16 rows per block, a warp per row, one sweep over a row's parts for all 512 dims) serves steps of at
+    // most 16 rows and head counts so small that tiles of 64 rows would leave most SMs idle (16 heads x 32 rows: 16 blocks
+    // of 64 rows against 32 of 16), as long as its blocks still fit one wave.
+    const bool small = rows <= 16 || H * ((rows + 15) / 16) <= 128;
+    dim3 grid(H, small ? (rows + 15) / 16 : (rows + MT - 1) / MT);
     auto go = [&](auto kernel, auto* o) {
         return int(launch_pdl(kernel, grid, dim3(NUM_THREADS), SMEM_BYTES, st, *map, recs, row_seg_begin, n_parts, o, rows, H, att_row, status));
     };
-    const bool small = rows <= 16;
     if (dtype == 0)
         return small ? go(merge_outproj_tc5_kernel<__half, true>, static_cast<__half*>(out))
                      : go(merge_outproj_tc5_kernel<__half, false>, static_cast<__half*>(out));
