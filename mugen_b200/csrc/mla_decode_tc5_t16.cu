@@ -4,7 +4,8 @@
 // With 16 heads the head-major tiles of mla_decode_tc5.cu would be three quarters padding.  Here the page tile is the
 // A operand of BOTH contractions and the small matrices (queries, probabilities) are the B operands:
 //
-//   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims]; Q' of the row's head
+//   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims], in the four slices the QK
+//            issuers work on (each with its own barrier, so the score MMAs start while the rest of the page lands); Q' of the row's head
 //            group [16 heads][576] as 9 sub-tiles [16][64]
 //   QK       S^T[64 tok x 16 heads] = K[64 x 576] . Q'^T          36 x tcgen05.mma  M=64  N=16 K=16
 //                                     A = cache sub-tiles (K-major), B = Q' (K-major)
@@ -49,7 +50,7 @@ constexpr int OFF_KV = OFF_Q + Q_BYTES;
 constexpr int OFF_P = OFF_KV + KV_STAGES * KV_STAGE_BYTES;
 constexpr int OFF_MISC = OFF_P + P_BYTES;         // barriers, alpha, tmem base, abort flag
 constexpr int MISC_BYTES = 1024;
-constexpr int M_TMEM = 112, M_ABORT = 116, M_ALPHA = 128, M_HMAX = 256, M_LSUM = 768;   // alpha [16]; hmax [2][4][16]; lsum [4][16]
+constexpr int M_TMEM = 176, M_ABORT = 180, M_ALPHA = 192, M_HMAX = 256, M_LSUM = 768;   // alpha [16]; hmax [2][4][16]; lsum [4][16]
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // +1024: manual 1 KB alignment
 
 constexpr uint32_t TMEM_COLS = 128;
@@ -62,8 +63,10 @@ constexpr int SOFTMAX_THREADS = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
 
 // barrier slots inside the misc area (8 bytes each)
-enum { B_QFULL = 0, B_QEMPTY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL0, B_SFULL1,
+// KVFULL: one barrier per (stage, QK issuer): an issuer starts on its sub-tiles of a page as soon as they have landed
+enum { B_QFULL = 0, B_QEMPTY, B_KVFULL, B_KVEMPTY0 = B_KVFULL + KV_STAGES * N_QK, B_KVEMPTY1, B_SFULL0, B_SFULL1,
        B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY, B_OFULL, B_COUNT };
+static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
 
 
 struct SegInfo {
@@ -84,7 +87,8 @@ __device__ __forceinline__ SegInfo load_seg(const StepMeta& m, uint32_t seg) {
 
 template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_q,
+decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid_constant__ CUtensorMap map_sub,
+                      const __grid_constant__ CUtensorMap map_q,
                   uint32_t layer, uint32_t n_pages, StepMeta m, float* __restrict__ recs, uint32_t H,
                   float scale_log2, uint32_t* __restrict__ status)
 {
@@ -109,8 +113,7 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_c
         *abort_flag = 0;
         mbar_init(bar(B_QFULL), 1);
         mbar_init(bar(B_QEMPTY), N_QK);
-        mbar_init(bar(B_KVFULL0), 1);
-        mbar_init(bar(B_KVFULL1), 1);
+        for (int i = 0; i < KV_STAGES * N_QK; i++) mbar_init(bar(B_KVFULL + i), 1);
         mbar_init(bar(B_KVEMPTY0), N_PV);
         mbar_init(bar(B_KVEMPTY1), N_PV);
         mbar_init(bar(B_SFULL0), N_QK);
@@ -156,9 +159,16 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_c
                         atomicOr(status, ST_BAD_PAGE);
                         page = 0;
                     }
-                    mbar_expect_tx(bar(B_KVFULL0 + st), KV_STAGE_BYTES);
-                    const uint32_t dst = sKV + st * KV_STAGE_BYTES;
-                    tma_load_4d(dst, &map_kv, bar(B_KVFULL0 + st), 0, int(page * kPage), 0, int(layer));   // whole page
+                    // the page in the four slices the QK issuers work on: sub-tiles 0-2, 3-4, 5-6, 7-8
+                    const uint32_t dst = sKV + st * KV_STAGE_BYTES, fb = B_KVFULL + st * N_QK;
+                    mbar_expect_tx(bar(fb), 3 * SUB_BYTES);
+                    tma_load_4d(dst, &map_pair, bar(fb), 0, int(page * kPage), 0, int(layer));
+                    tma_load_3d(dst + 2 * SUB_BYTES, &map_sub, bar(fb), 128, int(page * kPage), int(layer));
+#pragma unroll
+                    for (int p = 1; p < N_QK; p++) {
+                        mbar_expect_tx(bar(fb + p), 2 * SUB_BYTES);
+                        tma_load_4d(dst + (1 + 2 * p) * SUB_BYTES, &map_pair, bar(fb + p), 0, int(page * kPage), 1 + 2 * p, int(layer));
+                    }
                 }
                 nseg++;
             }
@@ -192,7 +202,7 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_c
             for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
                 const uint32_t st = t % KV_STAGES;
                 if (is_qk) {
-                    ok = mbar_wait(bar(B_KVFULL0 + st), (t / KV_STAGES) & 1, abort_flag, status) &&
+                    ok = mbar_wait(bar(B_KVFULL + st * N_QK + part), (t / KV_STAGES) & 1, abort_flag, status) &&
                          mbar_wait(bar(B_SEMPTY0), (t & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     tc_fence_after();
@@ -459,10 +469,10 @@ int launch_decode_tc5_t16(int dtype, const void* tmaps, uint32_t layer, uint32_t
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(m.ctas, (H + HG - 1) / HG);
     if (dtype == 0)
-        decode_tc5_t16_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries16], layer, n_pages, m,
+        decode_tc5_t16_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolV], maps[kMapPoolSub], maps[kMapQueries16], layer, n_pages, m,
                                                                         recs, H, scale_log2, status);
     else
-        decode_tc5_t16_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries16], layer,
+        decode_tc5_t16_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolV], maps[kMapPoolSub], maps[kMapQueries16], layer,
                                                                                n_pages, m, recs, H, scale_log2, status);
     return int(cudaGetLastError());
 }

@@ -31,7 +31,7 @@ int launch_decode_tc5(int dtype, const void* tmaps, uint32_t layer, uint32_t n_p
 int decode_tc5_configure();   // sets the kernel's attributes on the current device
 
 // The transposed form for narrow head counts (mla_decode_tc5_t16.cu): tokens are the M rows, groups of 16 heads the N
-// columns; grid (persistent blocks, ceil(H/16)).  Uses kMapPoolPage and kMapQueries16.
+// columns; grid (persistent blocks, ceil(H/16)).  Uses kMapPoolV, kMapPoolSub and kMapQueries16.
 int launch_decode_tc5_t16(int dtype, const void* tmaps, uint32_t layer, uint32_t n_pages, const StepMeta& m, float* recs,
                           uint32_t H, uint32_t* status, cudaStream_t st);
 int decode_tc5_t16_configure();
