@@ -4,8 +4,9 @@
 // With 16 heads the head-major tiles of mla_decode_tc5.cu would be three quarters padding.  Here the page tile is the
 // A operand of BOTH contractions and the small matrices (queries, probabilities) are the B operands:
 //
-//   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims], in the four slices the QK
-//            issuers work on (each with its own barrier, so the score MMAs start while the rest of the page lands); Q' of the row's head
+//   TMA      page tile [64 tok][576] -> shared memory as 9 swizzled sub-tiles [64 tok][64 dims]: four pairs into a ring of
+//            11 pair slots and the rope sub-tile into a ring of 3, each with its own barriers (the score MMAs start while
+//            the rest of the page lands, and 1.75 pages can be on their way while one is consumed); Q' of the row's head
 //            group [16 heads][576] as 9 sub-tiles [16][64]
 //   QK       S^T[64 tok x 16 heads] = K[64 x 576] . Q'^T          36 x tcgen05.mma  M=64  N=16 K=16
 //                                     A = cache sub-tiles (K-major), B = Q' (K-major)
@@ -38,20 +39,27 @@ constexpr int TILE = 64;                          // tokens per tile = one page
 constexpr int HG = 16;                            // heads per block
 constexpr int NSUB = kRow / 64;                   // 9 sub-tiles of 64 dims
 constexpr int SUB_BYTES = TILE * 128;             // 8 KB
-constexpr int KV_STAGE_BYTES = NSUB * SUB_BYTES;  // 73,728
-constexpr int KV_STAGES = 2;
+// A page does not sit in one stage buffer: its eight sub-tiles of latent dims are four PAIRS (one 128-dim chunk of O^T
+// each, 16 KB) in a ring of 11 pair slots, its rope sub-tile goes to a ring of three.  Two whole pages plus three quarters
+// of a third fit beside Q' and P, so up to 1.75 pages are on their way while one is consumed (two whole-page buffers,
+// the most that fits as stages, leave one load in flight and the kernel waiting for it: 0.75 of the measured HBM peak).
+constexpr int PAIR_BYTES = 2 * SUB_BYTES;         // 16 KB: sub-tiles 2i, 2i+1 of a page
+constexpr int N_PAIR_SLOTS = 11, N_ROPE_SLOTS = 3;
 // No L2 prefetch ahead of the loads: measured on 16 heads x 32 sequences x 8192 tokens, prefetching 4 / 8 pages ahead
 // (tensor-map or linear) takes the kernel from 59 us to 77 / 88 us.
 constexpr int Q_SUB = HG * 128;                   // 2,048: [16 heads][64 dims]
 constexpr int Q_BYTES = NSUB * Q_SUB;             // 18,432
 constexpr int P_BYTES = HG * 128;                 // 2,048: [16 heads][64 tok]
 constexpr int OFF_Q = 0;
-constexpr int OFF_KV = OFF_Q + Q_BYTES;
-constexpr int OFF_P = OFF_KV + KV_STAGES * KV_STAGE_BYTES;
+constexpr int OFF_PAIRS = OFF_Q + Q_BYTES;
+constexpr int OFF_ROPE = OFF_PAIRS + N_PAIR_SLOTS * PAIR_BYTES;
+constexpr int OFF_P = OFF_ROPE + N_ROPE_SLOTS * SUB_BYTES;
 constexpr int OFF_MISC = OFF_P + P_BYTES;         // barriers, alpha, tmem base, abort flag
-constexpr int MISC_BYTES = 1024;
-constexpr int M_TMEM = 176, M_ABORT = 180, M_ALPHA = 192, M_HMAX = 256, M_LSUM = 768;   // alpha [16]; hmax [2][4][16]; lsum [4][16]
+constexpr int MISC_BYTES = 1280;
+constexpr int M_TMEM = 304, M_ABORT = 308, M_ALPHA = 320, M_HMAX = 384, M_LSUM = 896;   // alpha [16]; hmax [2][4][16]; lsum [4][16]
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;   // +1024: manual 1 KB alignment
+static_assert(SMEM_BYTES <= 232448, "over the shared memory of one block");
+static_assert(OFF_PAIRS % 1024 == 0 && OFF_ROPE % 1024 == 0 && OFF_P % 1024 == 0, "swizzled tiles need 1 KB alignment");
 
 constexpr uint32_t TMEM_COLS = 128;
 constexpr uint32_t COL_O = 0;                     // 4 chunks of 128 dims x 16 head columns
@@ -63,9 +71,12 @@ constexpr int SOFTMAX_THREADS = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units
 
 // barrier slots inside the misc area (8 bytes each)
-// KVFULL: one barrier per (stage, QK issuer): an issuer starts on its sub-tiles of a page as soon as they have landed
-enum { B_QFULL = 0, B_QEMPTY, B_KVFULL, B_KVEMPTY0 = B_KVFULL + KV_STAGES * N_QK, B_KVEMPTY1, B_SFULL0, B_SFULL1,
-       B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY, B_OFULL, B_COUNT };
+// one full / empty barrier per pair slot and per rope slot: QK issuer i works on pair i of a page as soon as it has landed
+// (issuer 3 also on the rope sub-tile); a pair slot is free again when the PV MMAs of its chunk complete, a rope slot
+// when the score MMAs on it complete
+enum { B_QFULL = 0, B_QEMPTY, B_KF, B_KE = B_KF + N_PAIR_SLOTS, B_RF = B_KE + N_PAIR_SLOTS, B_RE = B_RF + N_ROPE_SLOTS,
+       B_SFULL0 = B_RE + N_ROPE_SLOTS, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PEMPTY, B_OFULL, B_COUNT };
+static_assert(N_QK == 4 && N_PV == 2, "the split of a page over the issuers below");
 static_assert(B_COUNT * 8 <= M_TMEM, "barriers overflow their area");
 
 
@@ -96,7 +107,7 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm = smem_raw + (base - raw);
-    const uint32_t sQ = base + OFF_Q, sKV = base + OFF_KV, sP = base + OFF_P;
+    const uint32_t sQ = base + OFF_Q, sPairs = base + OFF_PAIRS, sRope = base + OFF_ROPE, sP = base + OFF_P;
     const uint32_t sBar = base + OFF_MISC;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + M_TMEM);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + M_ABORT);
@@ -113,9 +124,7 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid
         *abort_flag = 0;
         mbar_init(bar(B_QFULL), 1);
         mbar_init(bar(B_QEMPTY), N_QK);
-        for (int i = 0; i < KV_STAGES * N_QK; i++) mbar_init(bar(B_KVFULL + i), 1);
-        mbar_init(bar(B_KVEMPTY0), N_PV);
-        mbar_init(bar(B_KVEMPTY1), N_PV);
+        for (int i = 0; i < 2 * N_PAIR_SLOTS + 2 * N_ROPE_SLOTS; i++) mbar_init(bar(B_KF + i), 1);
         mbar_init(bar(B_SFULL0), N_QK);
         mbar_init(bar(B_SFULL1), N_QK);
         mbar_init(bar(B_SEMPTY0), SOFTMAX_THREADS);
@@ -150,25 +159,26 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid
                 mbar_expect_tx(bar(B_QFULL), Q_BYTES);
                 tma_load_3d(sQ, &map_q, bar(B_QFULL), 0, int(s.row * H + h0), 0);          // all 9 sub-tiles in one box
                 const uint32_t* tbl = m.tables + m.seq_tbl_off[m.row_seq[s.row]];
-                for (uint32_t j = 0; j < s.n_tiles; j++, t++) {
-                    const uint32_t st = t % KV_STAGES;
-                    ok = mbar_wait(bar(B_KVEMPTY0 + st), ((t / KV_STAGES) & 1) ^ 1, abort_flag, status);
-                    if (!ok) break;
+                for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
                     uint32_t page = tbl[s.page_begin + j];
                     if (page >= n_pages) {
                         atomicOr(status, ST_BAD_PAGE);
                         page = 0;
                     }
-                    // the page in the four slices the QK issuers work on: sub-tiles 0-2, 3-4, 5-6, 7-8
-                    const uint32_t dst = sKV + st * KV_STAGE_BYTES, fb = B_KVFULL + st * N_QK;
-                    mbar_expect_tx(bar(fb), 3 * SUB_BYTES);
-                    tma_load_4d(dst, &map_pair, bar(fb), 0, int(page * kPage), 0, int(layer));
-                    tma_load_3d(dst + 2 * SUB_BYTES, &map_sub, bar(fb), 128, int(page * kPage), int(layer));
-#pragma unroll
-                    for (int p = 1; p < N_QK; p++) {
-                        mbar_expect_tx(bar(fb + p), 2 * SUB_BYTES);
-                        tma_load_4d(dst + (1 + 2 * p) * SUB_BYTES, &map_pair, bar(fb + p), 0, int(page * kPage), 1 + 2 * p, int(layer));
+#pragma unroll 1
+                    for (uint32_t i = 0; i < 4 && ok; i++) {          // pair i of page t: the (4t + i)-th use of the pair ring
+                        const uint32_t u = 4 * t + i, slot = u % N_PAIR_SLOTS;
+                        ok = mbar_wait(bar(B_KE + slot), ((u / N_PAIR_SLOTS) & 1) ^ 1, abort_flag, status);
+                        if (!ok) break;
+                        mbar_expect_tx(bar(B_KF + slot), PAIR_BYTES);
+                        tma_load_4d(sPairs + slot * PAIR_BYTES, &map_pair, bar(B_KF + slot), 0, int(page * kPage), int(2 * i), int(layer));
                     }
+                    if (!ok) break;
+                    const uint32_t rs = t % N_ROPE_SLOTS;
+                    ok = mbar_wait(bar(B_RE + rs), ((t / N_ROPE_SLOTS) & 1) ^ 1, abort_flag, status);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(B_RF + rs), SUB_BYTES);
+                    tma_load_3d(sRope + rs * SUB_BYTES, &map_sub, bar(B_RF + rs), kRank, int(page * kPage), int(layer));
                 }
                 nseg++;
             }
@@ -179,19 +189,15 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid
         // far more than the tensor core needs for these small shapes (N = 64, K = 16), so one
         // issuer leaves the pipe mostly idle.  Six warps issue concurrently, each into its own
         // accumulators: warps 1-4 split the 36 k-steps of QK into four partial score tiles
-        // (sub-tiles 0-2, 3-4, 5-6, 7-8; the softmax adds them), warps 5-6 take two of the four
+        // (sub-tile pairs 0-1, 2-3, 4-5, 6-7 + rope; the softmax adds them), warps 5-6 take two of the four
         // 128-dim chunks of O^T each.  The warp runs the loop uniformly (operands stay in uniform
         // registers) and one elected lane issues.
         constexpr uint32_t IDESC_QK = instr_desc(Fmt<T>::v, TILE, HG, 0, 0);          // M = 64 tokens, N = 16 heads
         constexpr uint32_t IDESC_PV = instr_desc(Fmt<T>::v, 128, HG, 1, 0);
         constexpr uint32_t HI = desc_hi(1024);          // every operand: 8-row groups 1024 B apart
-        static_assert(KV_STAGES == 2, "descriptor bases below assume two cache stages");
         const bool is_qk = warp <= N_QK;
         const uint32_t part = is_qk ? warp - 1 : warp - 1 - N_QK;
-        const int c_lo = part == 0 ? 0 : 1 + 2 * int(part), c_hi = 3 + 2 * int(part);   // QK sub-tile range
         const uint32_t qk_b = desc_lo(sQ, 16);          // Q' (K-major), the B operand here
-        const uint32_t kv_k0 = desc_lo(sKV, 16), kv_k1 = desc_lo(sKV + KV_STAGE_BYTES, 16);                 // tile as K
-        const uint32_t kv_v0 = desc_lo(sKV, SUB_BYTES), kv_v1 = desc_lo(sKV + KV_STAGE_BYTES, SUB_BYTES);   // tile as V^T
         const uint32_t pv_b = desc_lo(sP, 16);          // P (K-major)
         uint32_t t = 0, nseg = 0;
         bool ok = true;
@@ -200,44 +206,51 @@ decode_tc5_t16_kernel(const __grid_constant__ CUtensorMap map_pair, const __grid
             if (s.n_tiles == 0) continue;
             if (is_qk) ok = mbar_wait(bar(B_QFULL), nseg & 1, abort_flag, status);
             for (uint32_t j = 0; j < s.n_tiles && ok; j++, t++) {
-                const uint32_t st = t % KV_STAGES;
                 if (is_qk) {
-                    ok = mbar_wait(bar(B_KVFULL + st * N_QK + part), (t / KV_STAGES) & 1, abort_flag, status) &&
+                    // QK issuer i: pair i of the page (sub-tiles 2i, 2i+1); issuer 3 also the rope sub-tile
+                    const uint32_t u = 4 * t + part, slot = u % N_PAIR_SLOTS, rs = t % N_ROPE_SLOTS;
+                    ok = mbar_wait(bar(B_KF + slot), (u / N_PAIR_SLOTS) & 1, abort_flag, status) &&
+                         (part != 3 || mbar_wait(bar(B_RF + rs), (t / N_ROPE_SLOTS) & 1, abort_flag, status)) &&
                          mbar_wait(bar(B_SEMPTY0), (t & 1) ^ 1, abort_flag, status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a0 = st ? kv_k1 : kv_k0;
+                    const uint32_t a0 = desc_lo(sPairs + slot * PAIR_BYTES, 16), ar = desc_lo(sRope + rs * SUB_BYTES, 16);
                     const uint32_t d = tmem + COL_S + part * HG;
                     if (elect_one()) {
 #pragma unroll
-                        for (int c = 0; c < NSUB; c++) {
-                            if (c >= c_lo && c < c_hi) {
+                        for (int cc = 0; cc < 2; cc++)
 #pragma unroll
-                                for (int k = 0; k < 4; k++)
-                                    tc_mma(d, a0 + ((c * SUB_BYTES + k * 32) >> 4), HI, qk_b + ((c * Q_SUB + k * 32) >> 4),
-                                           HI, IDESC_QK, (c == c_lo && k == 0) ? 0u : 1u);
-                            }
+                            for (int k = 0; k < 4; k++)
+                                tc_mma(d, a0 + ((cc * SUB_BYTES + k * 32) >> 4), HI, qk_b + (((2 * part + cc) * Q_SUB + k * 32) >> 4),
+                                       HI, IDESC_QK, (cc == 0 && k == 0) ? 0u : 1u);
+                        if (part == 3) {
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                tc_mma(d, ar + ((k * 32) >> 4), HI, qk_b + ((8 * Q_SUB + k * 32) >> 4), HI, IDESC_QK, 1u);
+                            tc_commit(bar(B_RE + rs));
                         }
                         tc_commit(bar(B_SFULL0));
                         if (j + 1 == s.n_tiles) tc_commit(bar(B_QEMPTY));
                     }
                     __syncwarp();
                 } else {
+                    // PV issuer p: chunks 2p, 2p+1 of O^T = pairs 2p, 2p+1 of the page read MN-major.  The pairs have landed:
+                    // P exists only after all four score issuers waited for theirs.
                     ok = mbar_wait(bar(B_PFULL), t & 1, abort_flag, status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a0 = st ? kv_v1 : kv_v0;
                     const uint32_t fresh = j == 0 ? 0u : 1u;
                     if (elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < TILE / 16; k++)
+                        for (int cc = 0; cc < 2; cc++) {
+                            const uint32_t c = part * 2 + cc, slot = (4 * t + c) % N_PAIR_SLOTS;
+                            const uint32_t a0 = desc_lo(sPairs + slot * PAIR_BYTES, SUB_BYTES);
 #pragma unroll
-                            for (int cc = 0; cc < 2; cc++) {      // 128 latent dims per chunk = 2 sub-tiles
-                                const uint32_t c = part * 2 + cc;
-                                tc_mma(tmem + COL_O + c * HG, a0 + ((2 * c * SUB_BYTES + k * 2048) >> 4), HI,
-                                       pv_b + ((k * 32) >> 4), HI, IDESC_PV, k == 0 ? fresh : 1u);
-                            }
-                        tc_commit(bar(B_KVEMPTY0 + st));
+                            for (int k = 0; k < TILE / 16; k++)
+                                tc_mma(tmem + COL_O + c * HG, a0 + ((k * 2048) >> 4), HI, pv_b + ((k * 32) >> 4), HI, IDESC_PV,
+                                       k == 0 ? fresh : 1u);
+                            tc_commit(bar(B_KE + slot));
+                        }
                         tc_commit(bar(B_PEMPTY));
                         if (j + 1 == s.n_tiles) tc_commit(bar(B_OFULL));
                     }
