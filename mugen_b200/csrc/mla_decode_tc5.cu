@@ -102,6 +102,7 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
     const uint32_t cta = blockIdx.x, h0 = blockIdx.y * HG;
     const uint32_t seg_begin = m.cta_seg_begin[cta], seg_end = m.cta_seg_begin[cta + 1];
 
+    grid_launch_dependents();
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar(B_QFULL), 1);
@@ -129,6 +130,9 @@ decode_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    // queries, new cache rows and the state records belong to earlier kernels of the stream (the step's metadata does not:
+    // it was uploaded before the first of them started)
+    grid_dependency_wait();
 
     if (warp == 0) {
         // ===================== TMA producer =====================
@@ -458,12 +462,10 @@ int launch_decode_tc5(int dtype, const void* tmaps, uint32_t layer, uint32_t n_p
     const float scale_log2 = 1.4426950408889634f / sqrtf(float(kQDim));
     dim3 grid(m.ctas, (H + HG - 1) / HG);
     if (dtype == 0)
-        decode_tc5_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries], layer, n_pages, m,
-                                                                        recs, H, scale_log2, status);
-    else
-        decode_tc5_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(maps[kMapPoolPage], maps[kMapQueries], layer,
-                                                                               n_pages, m, recs, H, scale_log2, status);
-    return int(cudaGetLastError());
+        return int(launch_pdl(decode_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolPage], maps[kMapQueries],
+                              layer, n_pages, m, recs, H, scale_log2, status));
+    return int(launch_pdl(decode_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, maps[kMapPoolPage],
+                          maps[kMapQueries], layer, n_pages, m, recs, H, scale_log2, status));
 }
 
 }  // namespace mla
