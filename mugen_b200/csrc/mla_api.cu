@@ -653,8 +653,8 @@ int mla_create(const mla_config* cfg, mla_ctx** out)
     // streams the cache once per 64 heads (measured at 32 heads, 64 sequences x 8192 tokens: 128 us against 186 us for
     // two passes of the 16-column form and 300 us for mma.sync)
     c->kernel = cfg->kernel != MLA_KERNEL_AUTO ? cfg->kernel
-              : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? MLA_KERNEL_TCGEN05_PAIR128
-              : cfg->n_heads > 16 ? MLA_KERNEL_TCGEN05 : MLA_KERNEL_TCGEN05_T16;
+              : (cfg->n_heads % 128 == 0 && c->sm_count % 2 == 0) ? uint32_t(MLA_KERNEL_TCGEN05_PAIR128)
+              : cfg->n_heads > 16 ? uint32_t(MLA_KERNEL_TCGEN05) : uint32_t(MLA_KERNEL_TCGEN05_T16);
     const uint32_t H = cfg->n_heads;
     if (c->kernel == MLA_KERNEL_TCGEN05_PAIR128) c->workers = std::max<uint32_t>(1, (c->sm_count / 2) / ((H + 127) / 128));
     else if (c->kernel == MLA_KERNEL_TCGEN05) c->workers = std::max<uint32_t>(1, c->sm_count / ((H + 63) / 64));

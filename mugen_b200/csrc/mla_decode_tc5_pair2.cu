@@ -154,7 +154,8 @@ decode_tc5_pair128_kernel(const __grid_constant__ CUtensorMap map_sub, const __g
     if (warp == 0) {
         if (lane == 0) {
             *abort_flag = 0;
-            need_flag[0] = need_flag[1] = 0;
+            need_flag[0] = 0;
+            need_flag[1] = 0;
         }
         if (lane < B_COUNT) {
             const int i = int(lane);
