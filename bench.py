@@ -45,7 +45,7 @@ METRIC, UNIT = "mla_decode_tokens_per_s", "tokens/s"
 # The figure belongs to one version of the kernel's source: it is reported only while that file still hashes to the
 # value below (otherwise `traffic` is null until the capture is repeated).
 NCU_TRAFFIC = {"kernel": "tcgen05-pair128", "source": "mugen_b200/csrc/mla_decode_tc5_pair2.cu",
-               "source_sha256_16": "b8d4546c35b93d5f", "bytes_per_launch": 1.2640e9}
+               "source_sha256_16": "b8d4546c35b93d5f", "bytes_per_launch": 1.2647e9}
 # The attention kernel is timed live by CUDA events inside the library on every 7th launch of the timed region
 # (7 is coprime to 61 layers, so every layer gets sampled over the steps): an event between two kernels stops
 # the next one from becoming resident while the previous drains, and bracketing every launch would slow the
