@@ -29,17 +29,22 @@ namespace {
 using namespace tc5;
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 4;
 constexpr int TILE_BYTES = BM * BK * 2;                  // 16,384 (A and W tiles alike)
-constexpr int OFF_MISC = STAGES * 2 * TILE_BYTES;        // 131,072
-constexpr int SMEM_BYTES = OFF_MISC + 128 + 1024;        // barriers + slack for 1 KB alignment
+// Two shapes of the same kernel.  Four stages, one block per SM: long K (the decode-time projections, split-K).  Two
+// stages, three blocks per SM: short K and many output tiles (the prefill expansion, K = 512): a tile is then a chain
+// load -> 32 MMAs -> epilogue of a few microseconds with nothing to overlap inside one block, and three blocks per SM take
+// turns on the tensor pipe (12288 x 16384 x 512: 502 us with one block per SM).
+constexpr int off_misc(int stages) { return stages * 2 * TILE_BYTES; }
+constexpr int smem_bytes(int stages) { return off_misc(stages) + 128 + 1024; }      // barriers + slack for 1 KB alignment
+constexpr int MAX_STAGES = 4;
 constexpr int NUM_THREADS = 32 * 6;
 constexpr uint32_t TMEM_COLS = 128;
 
 // out_f32 != nullptr: float partials [z][M][N]; else storage-type output [M][N]
-template <typename T>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, T* __restrict__ out,
+template <typename T, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, STAGES == 2 ? 3 : 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_c, uint32_t tile_store, T* __restrict__ out,
                 float* __restrict__ out_f32, uint32_t M, uint32_t N, uint32_t K, uint32_t k_blocks_per_split,
                 uint32_t* __restrict__ status)
 {
@@ -47,6 +52,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t raw = smem_u32(gemm_smem);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm = gemm_smem + (base - raw);
+    constexpr int OFF_MISC = off_misc(STAGES);
+    static_assert(STAGES <= MAX_STAGES, "barrier slots");
     const uint32_t bar0 = base + OFF_MISC;                       // full[STAGES], empty[STAGES], done
     auto full = [&](int s) { return bar0 + 8u * uint32_t(s); };
     auto empty = [&](int s) { return bar0 + 8u * uint32_t(STAGES + s); };
@@ -120,6 +127,22 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int i = 0; i < 32; i++) v[i] = 0u;              // an empty K slice contributes zeros
                 }
                 const uint32_t col = n0 + c * 32;
+                if (tile_store) {
+                    // The tile goes out through shared memory (the pipeline buffers are free: every MMA has completed) as two
+                    // boxes of 64 columns x 128 rows in the 128-byte swizzle, and TMA writes whole rows of a box; a thread
+                    // storing its own 64 bytes per row piece reaches a third of that rate on 400 MB of output.
+                    const uint32_t r = q4 * 32 + lane;
+                    unsigned char* box = sm + (c / 2) * TILE_BYTES + r * 128;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            pk[j] = Elem<T>::pack2(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                        *reinterpret_cast<uint4*>(box + ((((c % 2) * 4 + i) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                    continue;
+                }
                 if (row >= M || col >= N) continue;
                 if (out_f32) {
                     float* dst = out_f32 + (size_t(blockIdx.z) * M + row) * N + col;
@@ -146,6 +169,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int i = 0; i < 32 && col + i < N; i++) dst[i] = Elem<T>::from_f32(__uint_as_float(v[i]));
                     }
                 }
+            }
+        }
+        if (tile_store) {                        // outside the test of `ok`: the barrier is for all four epilogue warps
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("barrier.cta.sync 1, 128;\n" ::: "memory");
+            if (warp == 2 && ok && *abort_flag == 0 && elect_one()) {
+                tma_store_2d(&map_c, base, int(n0), int(m0));
+                tma_store_2d(&map_c, base + TILE_BYTES, int(n0 + 64), int(m0));
+                tma_store_commit_and_wait_read();
             }
         }
     }
@@ -258,8 +290,10 @@ bool make_map(CUtensorMap* map, int dtype, const void* ptr, uint64_t rows, uint6
 
 int gemm_tc5_configure()
 {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<__half, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc5_kernel<__nv_bfloat16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc5_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc5_kernel<__nv_bfloat16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2));
     return int(e);
 }
 
@@ -279,17 +313,26 @@ int launch_gemm_tc5(int dtype, const void* A, uint32_t lda, const void* W, uint3
                     void* out, float* partial, uint32_t splits, uint32_t* status, cudaStream_t st)
 {
     if (M == 0 || N == 0) return 0;
-    alignas(64) CUtensorMap ma, mw;
+    alignas(64) CUtensorMap ma, mw, mc;
     if (!make_map(&ma, dtype, A, M, K, lda) || !make_map(&mw, dtype, W, N, K, ldw)) return -1;
+    // storage-type output with rows that TMA can address: the epilogue stores tiles (see the kernel)
+    const uint32_t tile_store = (!partial && out && N % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+                                 make_map(&mc, dtype, out, M, N, N)) ? 1u : 0u;
+    if (!tile_store) mc = ma;
     const uint32_t kb = (K + BK - 1) / BK;
     splits = std::max(1u, std::min(splits, kb));
     const uint32_t per = (kb + splits - 1) / splits;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
+    const bool many_short = per <= 8 && size_t(grid.x) * grid.y * grid.z >= 1024;      // see the note on the two shapes
+    auto go = [&](auto kernel, int stages, auto* o) {
+        return int(launch_pdl(kernel, grid, dim3(NUM_THREADS), size_t(smem_bytes(stages)), st, ma, mw, mc, tile_store, o, partial, M, N, K,
+                              per, status));
+    };
     if (dtype == 0)
-        return int(launch_pdl(gemm_tc5_kernel<__half>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, ma, mw, static_cast<__half*>(out),
-                              partial, M, N, K, per, status));
-    return int(launch_pdl(gemm_tc5_kernel<__nv_bfloat16>, grid, dim3(NUM_THREADS), SMEM_BYTES, st, ma, mw,
-                          static_cast<__nv_bfloat16*>(out), partial, M, N, K, per, status));
+        return many_short ? go(gemm_tc5_kernel<__half, 2>, 2, static_cast<__half*>(out))
+                          : go(gemm_tc5_kernel<__half, 4>, 4, static_cast<__half*>(out));
+    return many_short ? go(gemm_tc5_kernel<__nv_bfloat16, 2>, 2, static_cast<__nv_bfloat16*>(out))
+                      : go(gemm_tc5_kernel<__nv_bfloat16, 4>, 4, static_cast<__nv_bfloat16*>(out));
 }
 
 // mode 0 store, 1 RMSNorm(w, eps), 2 residual add (res); see gemm_finalize_kernel
