@@ -10,8 +10,8 @@
 // prefill path (M = tokens, K = 512).
 //
 // One block per 128 x 128 output tile and K slice: warp 0 = TMA producer (A and W tiles of 128 rows x 64 values, 128-byte
-// swizzle, four stages), warp 1 = MMA issuer (tcgen05.mma M128 N128 K16, cta_group::1), warps 2-5 = epilogue (TMEM ->
-// registers -> global).  Rows and columns beyond M / N / K are zero-filled by TMA and never stored.  With split-K
+// swizzle, four or two stages), warp 1 = MMA issuer (tcgen05.mma M128 N128 K16, cta_group::1), warps 2-5 = epilogue (TMEM ->
+// registers -> shared memory -> TMA tile store for storage-type output; TMEM -> registers -> global for float partials).  Rows and columns beyond M / N / K are zero-filled by TMA and never stored.  With split-K
 // (few output tiles, long K: the decode-time projections) every slice writes float partial sums and a second kernel
 // adds them and applies what follows the projection in the reference: rounding to the storage type, then optionally
 // RMSNorm with a weight (q_a_norm) or the residual add.
