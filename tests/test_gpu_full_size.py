@@ -1,4 +1,4 @@
-"""GPU parity at the benchmark's full shapes (128 heads, bf16; contexts of 16384 and 131072 tokens),
+"""GPU parity at the benchmark's full shapes (128 heads, bf16; contexts of 16384 and 131072 tokens; 16 heads, fp16, ctx 8192),
 through the C ABI.  The CPU checker is too slow for whole batches at these sizes, so most checks are
 properties that do not depend on the size — the same logical cache under two page permutations, a
 KV-range split against the unsplit sequence, a prefill chunk against single decode rows — with
@@ -95,6 +95,51 @@ def test_ctx16384_decode_step_page_permutation_and_checker(torch, oracle):
     want = oracle.attention_batch(qh, fulls, [S + 1] * B, wk, wv, synth.W_BF16, H, DT, min(B, os.cpu_count() or 1))
     for b in range(B):                                       # every sequence, all 128 heads
         _close(outs[0][b], want[b], f"sequence {b} at ctx {S + 1}")
+
+
+def test_v2lite_shape_decode_step_at_size_all_sequences_against_the_checker(torch, oracle):
+    """configs[1] shape: 16 heads, 32 sequences of ctx 8192, fp16 cache, pages in a random permutation, one decode step
+    through mla_step_layers (the 16-column tcgen05 kernel).  Every sequence and head against the CPU attention; the
+    appended rows bit for bit; the same logical caches under a second page permutation give identical bits."""
+    from mugen_b200.mla import MlaContext
+    Hs, dt, B, S = 16, synth.DT_F16, 32, 8191
+    rng = np.random.default_rng(21)
+    wk = synth.to_bits(rng.standard_normal((Hs * 128, 512), np.float32) * np.float32(0.02), dt)
+    wv = synth.to_bits(rng.standard_normal((Hs * 128, 512), np.float32) * np.float32(0.02), dt)
+    nw = synth.to_bits((1.0 + 0.1 * rng.standard_normal(512)).astype(np.float32), dt)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2121)
+    f16 = lambda shape, scale=1.0: (torch.randn(shape, device="cuda", dtype=torch.float32, generator=g) * scale).to(torch.float16).view(torch.int16)
+    cache, kv, q = f16((B, S, 576)), f16((B, 576)), f16((B, Hs, 192), 0.9)
+    outs, rows = [], []
+    for shuffle in (5, 91):
+        ctx = MlaContext(n_layers=1, n_heads=Hs, dtype=dt, n_pages=B * 129 + 16, max_seqs=B, max_seq_len=S + 65,
+                         kernel=capi.KERNEL_AUTO, **YARN)
+        ctx.shuffle_free_pages(shuffle)
+        ctx.set_layer_weights(0, wk, wv, synth.W_F16, nw)
+        seqs = []
+        for b in range(B):
+            sq = ctx.seq_create()
+            ctx.write_rows(0, sq, 0, cache[b])
+            ctx.advance_seq_len(sq, S)
+            seqs.append(sq)
+        out = torch.zeros((B, Hs, 128), dtype=torch.int16, device="cuda")
+        ctx.step_begin(seqs)
+        ctx.step_layers(0, 1, kv[None], q[None], out[None])
+        ctx.step_end()
+        assert ctx.status() == 0 and ctx.kernel_name() == "tcgen05-t16"
+        outs.append(_bits(out).copy())
+        rows.append(np.stack([ctx.read_rows(0, seqs[b], S, 1)[0] for b in range(B)]))
+        ctx.close()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(rows[0], rows[1])
+    want_rows = oracle.append_rows(_bits(kv), [S] * B, nw, YARN["rms_norm_eps"], 40.0, 4096, 10000.0, dt)
+    assert np.array_equal(rows[0], want_rows)
+    qh, ch = _bits(q), _bits(cache)
+    fulls = [np.concatenate([ch[b], want_rows[b:b + 1]]) for b in range(B)]
+    want = oracle.attention_batch(qh, fulls, [S + 1] * B, wk, wv, synth.W_F16, Hs, dt, min(B, os.cpu_count() or 1))
+    for b in range(B):
+        mx, rl = synth.error_norms(outs[0][b], want[b], dt, dt)
+        assert mx <= MAX_ABS and rl <= REL_L2, f"sequence {b}: max-abs {mx:.3e}, rel-L2 {rl:.3e}"
 
 
 def test_ctx131072_kv_range_split_equals_whole(torch, oracle):
